@@ -4,6 +4,7 @@ caller chooses for generation (GeneratorParams)."""
 from gllm_b200.config.generator_params import GeneratorParams
 from gllm_b200.config.guvetar_config import GuvetarConfig
 from gllm_b200.config.llama_config import LlamaConfig, RopeScaling
+from gllm_b200.config.mifidra_config import MifidraConfig
 from gllm_b200.config.model_config import ConfigError, ModelConfig, load_config
 from gllm_b200.config.registry import (
     ARCHITECTURES,
@@ -17,6 +18,7 @@ __all__ = [
     "ConfigError",
     "GuvetarConfig",
     "LlamaConfig",
+    "MifidraConfig",
     "ModelConfig",
     "RopeScaling",
     "load_config",

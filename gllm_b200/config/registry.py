@@ -37,6 +37,7 @@ def _ensure_builtin_loaded() -> None:
     # The built-in architectures register themselves on import.
     import gllm_b200.models.guvetar  # noqa: F401
     import gllm_b200.models.llama  # noqa: F401
+    import gllm_b200.models.mifidra  # noqa: F401
     import gllm_b200.models.rulunex  # noqa: F401
 
 

@@ -1,0 +1,250 @@
+// The gated delta rule: a matrix state per head that forgets per key channel and is corrected, not just added to,
+//   S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q,
+// with everything but the projections in fp32.  Three kernels:
+//   delta_prep         per token: the short causal convolution + SiLU of the q, k and v projections (over the
+//                      request's own earlier tokens and its convolution state), q and k made unit vectors per head
+//                      (q also times q_scale), the decays g = exp(-exp(A_log[h]) softplus(a + dt_bias)) and
+//                      beta = sigmoid(b);
+//   conv_state_update  per request: the last taps-1 inputs of the convolution become its new state;
+//   delta_rule         per (request, head, block of value columns): the recurrence, token after token.
+// Every value column of S obeys the same recurrence by itself (column c: s <- g s; u_c = beta (v_c - s.k);
+// s <- s + k u_c; o_c = s.q), so a column is shared by `lanes` threads that each keep DPT of its key channels
+// and add their parts of the two dot products by shuffles.  o_c is formed as (g s).q + u_c (k.q), which needs
+// one round of shuffles per token instead of two.  The state is stored column by column, [slots, heads, dv, dk],
+// as the other matrix recurrences store theirs.
+// The flat batch holds prompt portions beside single tokens: request r owns rows cu_q[r] .. cu_q[r+1]-1 and row
+// state_slots[r] of the state tensors, so a prompt may be cut anywhere.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+constexpr int DELTA_MAX_TAPS = 16;
+
+// x [n, >= channels] at x_stride: the projections' output, q | k | v channels first (qk_cols = 2 * kv_heads * dk,
+// then heads * dv).  Outputs fp32: qk [n, qk_cols], v [n, heads * dv], g [n, heads * dk], beta [n, heads].
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_prep_kernel(const T* __restrict__ x, int64_t x_stride, const float* __restrict__ conv_w,
+                  const float* __restrict__ conv_state, const int* __restrict__ positions,
+                  const int* __restrict__ token_row, const float* __restrict__ a_raw, int64_t a_stride,
+                  const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                  const float* __restrict__ b_raw, int64_t b_stride, float* __restrict__ qk, float* __restrict__ v,
+                  float* __restrict__ g, float* __restrict__ beta, int heads, int kv_heads, int dk, int dv, int taps,
+                  float unit_eps, float q_scale) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int qk_cols = 2 * kv_heads * dk, channels = qk_cols + heads * dv;
+  const int row = token_row[i], pos = positions[i];
+  // how many of the request's earlier tokens this batch holds right before row i (at most taps-1 matter)
+  int here = 0;
+  while (here < taps - 1 && i - here - 1 >= 0 && token_row[i - here - 1] == row && positions[i - here - 1] == pos - here - 1)
+    ++here;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {          // j tokens back
+      float val;
+      if (j <= here) {
+        val = to_float(x[(int64_t)(i - j) * x_stride + c]);
+      } else {
+        const int idx = taps - 1 - (j - here);   // the state holds the inputs before the batch's first, oldest first
+        val = conv_state[((int64_t)row * (taps - 1) + idx) * channels + c];
+      }
+      acc = fmaf(conv_w[(int64_t)c * taps + (taps - 1 - j)], val, acc);
+    }
+    sm[c] = acc / (1.0f + expf(-acc));
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < 2 * kv_heads; h += nwarps) {
+    float ss = 0.f;
+    for (int c = lane; c < dk; c += 32) ss = fmaf(sm[h * dk + c], sm[h * dk + c], ss);
+    ss = warp_sum(ss);
+    const float inv = (h < kv_heads ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
+    for (int c = lane; c < dk; c += 32) qk[(int64_t)i * qk_cols + h * dk + c] = sm[h * dk + c] * inv;
+  }
+  for (int c = threadIdx.x; c < heads * dv; c += blockDim.x) v[(int64_t)i * heads * dv + c] = sm[qk_cols + c];
+  for (int c = threadIdx.x; c < heads * dk; c += blockDim.x) {
+    const int h = c / dk;
+    g[(int64_t)i * heads * dk + c] = expf(-expf(A_log[h]) * softplusf_(a_raw[(int64_t)i * a_stride + c] + dt_bias[c]));
+  }
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) beta[(int64_t)i * heads + h] = sigmoidf_(b_raw[(int64_t)i * b_stride + h]);
+}
+
+// conv_state [slots, taps-1, channels] <- the last taps-1 of (old state ++ this step's inputs), per request.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_state_update_kernel(const T* __restrict__ x, int64_t x_stride, float* __restrict__ conv_state,
+                         const int* __restrict__ cu_q, const int* __restrict__ state_slots, int channels, int taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int t0 = cu_q[r], len = cu_q[r + 1] - t0;
+  const int keep = taps - 1;
+  float* cs = conv_state + (int64_t)state_slots[r] * keep * channels + c;
+  for (int j = 0; j < keep; ++j) {           // ascending: what is read lies at or behind what is written
+    const int ci = j + len;                  // index into (old state ++ inputs)
+    cs[(int64_t)j * channels] = ci < keep ? cs[(int64_t)ci * channels]
+                                          : to_float(x[(int64_t)(t0 + ci - keep) * x_stride + c]);
+  }
+}
+
+constexpr int DELTA_THREADS = 128;
+constexpr int DELTA_CHUNK = 16;
+
+template <int DPT>
+__global__ void __launch_bounds__(DELTA_THREADS)
+delta_rule_kernel(const float* __restrict__ qk, const float* __restrict__ v, const float* __restrict__ g,
+                  const float* __restrict__ beta, float* __restrict__ state, const int* __restrict__ cu_q,
+                  const int* __restrict__ state_slots, float* __restrict__ out, int heads, int kv_heads, int dk,
+                  int dv, int lanes) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  pdl_wait();
+  const int cols = DELTA_THREADS / lanes, dkp = lanes * DPT;
+  const int r = blockIdx.z, h = blockIdx.y, hg = h / (heads / kv_heads);
+  const int col = blockIdx.x * cols + threadIdx.x / lanes, sub = threadIdx.x % lanes;
+  const bool live = col < dv;
+  const int t0 = cu_q[r], t1 = cu_q[r + 1];
+  if (t1 <= t0) return;
+  float* qs = sm;                                   // [chunk][dkp]
+  float* ks = qs + DELTA_CHUNK * dkp;
+  float* gs = ks + DELTA_CHUNK * dkp;
+  float* vs = gs + DELTA_CHUNK * dkp;               // [chunk][cols]
+  float* bs = vs + DELTA_CHUNK * cols;              // [chunk]
+  float S[DPT];
+  float* sp = state + (((int64_t)state_slots[r] * heads + h) * dv + (live ? col : 0)) * dk;
+#pragma unroll
+  for (int e = 0; e < DPT; ++e) {
+    const int d = sub * DPT + e;
+    S[e] = live && d < dk ? sp[d] : 0.f;
+  }
+  const int qk_cols = 2 * kv_heads * dk;
+  for (int c0 = t0; c0 < t1; c0 += DELTA_CHUNK) {
+    const int tc = min(DELTA_CHUNK, t1 - c0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < tc * dkp; idx += DELTA_THREADS) {
+      const int t = idx / dkp, d = idx - t * dkp;
+      const bool ok = d < dk;
+      const int64_t tok = c0 + t;
+      qs[idx] = ok ? qk[tok * qk_cols + hg * dk + d] : 0.f;
+      ks[idx] = ok ? qk[tok * qk_cols + (kv_heads + hg) * dk + d] : 0.f;
+      gs[idx] = ok ? g[(tok * heads + h) * dk + d] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < tc * cols; idx += DELTA_THREADS) {
+      const int t = idx / cols, c = blockIdx.x * cols + (idx - t * cols);
+      vs[idx] = c < dv ? v[((int64_t)(c0 + t) * heads + h) * dv + c] : 0.f;
+    }
+    for (int t = threadIdx.x; t < tc; t += DELTA_THREADS) bs[t] = beta[(int64_t)(c0 + t) * heads + h];
+    __syncthreads();
+    for (int t = 0; t < tc; ++t) {
+      const float* qt = qs + t * dkp + sub * DPT;
+      const float* kt = ks + t * dkp + sub * DPT;
+      const float* gt = gs + t * dkp + sub * DPT;
+      float kk[DPT], qq[DPT];
+      float sk = 0.f, sq = 0.f, kq = 0.f;
+#pragma unroll
+      for (int e = 0; e < DPT; ++e) {
+        kk[e] = kt[e];
+        qq[e] = qt[e];
+        S[e] *= gt[e];
+        sk = fmaf(S[e], kk[e], sk);
+        sq = fmaf(S[e], qq[e], sq);
+        kq = fmaf(kk[e], qq[e], kq);
+      }
+      for (int o = lanes >> 1; o > 0; o >>= 1) {
+        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      }
+      const float u = bs[t] * (vs[t * cols + threadIdx.x / lanes] - sk);
+#pragma unroll
+      for (int e = 0; e < DPT; ++e) S[e] = fmaf(kk[e], u, S[e]);
+      if (sub == 0 && live) out[((int64_t)(c0 + t) * heads + h) * dv + col] = fmaf(u, kq, sq);
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int e = 0; e < DPT; ++e) {
+      const int d = sub * DPT + e;
+      if (d < dk) sp[d] = S[e];
+    }
+  }
+}
+
+inline int pow2_at_least(int n) {
+  int p = 1;
+  while (p < n) p <<= 1;
+  return p;
+}
+
+template <typename T>
+int delta_prep_launch(const T* x, int64_t x_stride, const float* conv_w, float* conv_state, const int* positions,
+                      const int* token_row, const int* cu_q, const int* state_slots, int num_requests,
+                      const float* a_raw, int64_t a_stride, const float* dt_bias, const float* A_log, const float* b_raw,
+                      int64_t b_stride, float* qk, float* v, float* g, float* beta, int n_tokens, int heads, int kv_heads,
+                      int dk, int dv, int taps, float unit_eps, float q_scale, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  const int channels = 2 * kv_heads * dk + heads * dv;
+  const size_t smem = sizeof(float) * (size_t)channels;
+  if (taps < 1 || taps > DELTA_MAX_TAPS || heads % kv_heads || smem > 200 * 1024 || num_requests > 65535)
+    return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  int rc = gllm_launch(delta_prep_kernel<T>, dim3(n_tokens), dim3(256), smem, stream, x, x_stride, conv_w,
+                       (const float*)conv_state, positions, token_row, a_raw, a_stride, dt_bias, A_log, b_raw, b_stride,
+                       qk, v, g, beta, heads, kv_heads, dk, dv, taps, unit_eps, q_scale);
+  if (rc != 0 || taps == 1 || num_requests <= 0) return rc;
+  return gllm_launch(conv_state_update_kernel<T>, dim3((channels + 255) / 256, num_requests), dim3(256), 0, stream, x,
+                     x_stride, conv_state, cu_q, state_slots, channels, taps);
+}
+
+int delta_rule_launch(const float* qk, const float* v, const float* g, const float* beta, float* state,
+                      const int* cu_q, const int* state_slots, float* out, int num_requests, int heads, int kv_heads,
+                      int dk, int dv, cudaStream_t stream) {
+  if (num_requests <= 0) return 0;
+  if (heads > 65535 || num_requests > 65535 || dk < 1 || dv < 1 || dk > 512 || heads % kv_heads)
+    return (int)cudaErrorInvalidValue;
+  const int dpt = dk <= 128 ? 4 : (dk <= 256 ? 8 : 16);
+  const int lanes = pow2_at_least((dk + dpt - 1) / dpt);
+  const int cols = DELTA_THREADS / lanes, dkp = lanes * dpt;
+  const size_t smem = sizeof(float) * (size_t)DELTA_CHUNK * (3 * dkp + cols + 1);
+  void (*kernel)(const float*, const float*, const float*, const float*, float*, const int*, const int*, float*, int, int,
+                 int, int, int) = dpt == 4 ? delta_rule_kernel<4> : (dpt == 8 ? delta_rule_kernel<8> : delta_rule_kernel<16>);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return gllm_launch(kernel, dim3((dv + cols - 1) / cols, heads, num_requests), dim3(DELTA_THREADS), smem, stream, qk, v,
+                     g, beta, state, cu_q, state_slots, out, heads, kv_heads, dk, dv, lanes);
+}
+}  // namespace
+
+#define GLLM_DELTA_EXPORTS(T, S)                                                                                       \
+  GLLM_API int gllm_delta_prep_##S(const T* x, int64_t x_stride, const float* conv_w, float* conv_state,               \
+                                   const int* positions, const int* token_row, const int* cu_q,                        \
+                                   const int* state_slots, int num_requests, const float* a_raw, int64_t a_stride,     \
+                                   const float* dt_bias, const float* A_log, const float* b_raw, int64_t b_stride,     \
+                                   float* qk, float* v, float* g, float* beta, int n_tokens, int heads, int kv_heads,  \
+                                   int dk, int dv, int taps, float unit_eps, float q_scale, cudaStream_t stream) {     \
+    return delta_prep_launch<T>(x, x_stride, conv_w, conv_state, positions, token_row, cu_q, state_slots,              \
+                                num_requests, a_raw, a_stride, dt_bias, A_log, b_raw, b_stride, qk, v, g, beta,        \
+                                n_tokens, heads, kv_heads, dk, dv, taps, unit_eps, q_scale, stream);                   \
+  }
+GLLM_DELTA_EXPORTS(float, f32)
+GLLM_DELTA_EXPORTS(__nv_bfloat16, bf16)
+
+GLLM_API int gllm_delta_rule(const float* qk, const float* v, const float* g, const float* beta, float* state,
+                             const int* cu_q, const int* state_slots, float* out, int num_requests, int heads,
+                             int kv_heads, int dk, int dv, int max_q_len, cudaStream_t stream) {
+  (void)max_q_len;
+  return delta_rule_launch(qk, v, g, beta, state, cu_q, state_slots, out, num_requests, heads, kv_heads, dk, dv, stream);
+}

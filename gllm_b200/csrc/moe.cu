@@ -1,0 +1,303 @@
+// Routed experts: every token is served by `top` of `experts` small gated feed-forwards.
+//   moe_route    per token (one warp): scores s = sigmoid(z) of the fp32 router logits; the choice is made on
+//                s + correction, optionally only among the experts of the `keep` best of `groups` equal groups of
+//                neighbours (a group's score: the sum of its two largest choice scores; experts of other groups
+//                count as minus infinity); the weights are the chosen experts' s (divided by their sum with
+//                `renorm`).  Ties go to the lower index.
+//   moe_align    (one block) sorts the (token, slot) pairs by expert: every expert's pairs form whole tiles of
+//                `tile_m` rows (the last one filled up with -1), so that a tile of the products below reads ONE
+//                expert's weights; writes the pair of every row, the expert of every tile and the tile count.
+//   moe_gemm     out[pair] = A[row of pair] @ W[expert]^T over the tiles; `gated`: W holds gate and up rows and
+//                the result is silu(gate) * up, rounded to T; otherwise the fp32 result itself.
+//   moe_combine  out[token] = sum over its slots, in slot order, of weight * result[pair] (+ a shared expert's
+//                result), rounded to T.
+// A pair's result does not depend on which other pairs share its tile or on the tile's place: every row is a dot
+// product over K in one fixed order.  Scores, choice, weights, accumulators and the combination are fp32.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) {
+      v = ov;
+      i = oi;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(32)
+moe_route_kernel(const float* __restrict__ logits, int64_t stride, const float* __restrict__ correction,
+                 int* __restrict__ ids, float* __restrict__ weights, int experts, int top, int groups, int keep,
+                 int renorm) {
+  extern __shared__ float sm[];
+  float* s = sm;                 // [experts] scores
+  float* c = s + experts;        // [experts] choice scores
+  float* gs = c + experts;       // [groups] group scores, then 1 = kept
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x, lane = threadIdx.x;
+  for (int e = lane; e < experts; e += 32) {
+    const float z = logits[(int64_t)i * stride + e];
+    const float v = 1.0f / (1.0f + expf(-z));
+    s[e] = v;
+    c[e] = v + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = experts / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float m1 = -CUDART_INF_F, m2 = -CUDART_INF_F;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = c[e];
+        if (v > m1) {
+          m2 = m1;
+          m1 = v;
+        } else if (v > m2) {
+          m2 = v;
+        }
+      }
+      gs[g] = per > 1 ? m1 + m2 : m1;
+    }
+    __syncwarp();
+    // the `keep` best groups, one after the other; a kept group is marked by +inf ... then turned into a flag
+    for (int r = 0; r < keep; ++r) {
+      float best = -CUDART_INF_F;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gs[g];
+        if (v != CUDART_INF_F && (v > best || bi == 0x7fffffff)) {
+          best = v;
+          bi = g;
+        }
+      }
+      warp_argmax(best, bi);
+      __syncwarp();
+      if (lane == 0 && bi < groups) gs[bi] = CUDART_INF_F;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (gs[e / per] != CUDART_INF_F) c[e] = -CUDART_INF_F;
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float best = -CUDART_INF_F;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = c[e];
+      if (v > best) {
+        best = v;
+        bi = e;
+      }
+    }
+    warp_argmax(best, bi);
+    __syncwarp();
+    if (bi >= experts) bi = 0;              // nothing left to choose (NaN logits): keep the indices in range
+    if (lane == 0) {
+      ids[(int64_t)i * top + r] = bi;
+      weights[(int64_t)i * top + r] = s[bi];
+      c[bi] = -CUDART_INF_F;
+    }
+    total += s[bi];
+    __syncwarp();
+  }
+  if (renorm) {
+    for (int r = lane; r < top; r += 32) weights[(int64_t)i * top + r] /= total;
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ ids, int* __restrict__ sorted, int* __restrict__ tile_expert,
+                 int* __restrict__ num_tiles, int n_pairs, int experts, int tile_m, int max_tiles) {
+  extern __shared__ int smi[];
+  int* counts = smi;                  // [experts]
+  int* first = counts + experts;      // [experts + 1] first row of every expert
+  int* cursor = first + experts + 1;  // [experts]
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = cursor[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < experts; ++e) {
+      first[e] = at;
+      at += (counts[e] + tile_m - 1) / tile_m * tile_m;
+    }
+    first[experts] = at;
+    num_tiles[0] = min(at / tile_m, max_tiles);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    for (int t = first[e] / tile_m; t < first[e + 1] / tile_m && t < max_tiles; ++t) tile_expert[t] = e;
+  for (int r = threadIdx.x; r < max_tiles * tile_m; r += blockDim.x) sorted[r] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e < 0 || e >= experts) continue;
+    const int row = first[e] + atomicAdd(&cursor[e], 1);
+    if (row < max_tiles * tile_m) sorted[row] = p;
+  }
+}
+
+constexpr int MG_M = 16, MG_N = 64, MG_K = 32, MG_THREADS = 128;
+
+// grid (max_tiles, ceil(n_cols / MG_N)).  A row of pair p: a + (p / a_div) * a_stride.  W of expert e: w + e *
+// w_expert_stride, rows of k columns; gated: up rows lie `up_offset` elements behind the gate rows.
+template <typename T>
+__global__ void __launch_bounds__(MG_THREADS)
+moe_gemm_kernel(const T* __restrict__ a, int64_t a_stride, int a_div, const T* __restrict__ w, int64_t w_expert_stride,
+                int64_t up_offset, const int* __restrict__ sorted, const int* __restrict__ tile_expert,
+                const int* __restrict__ num_tiles, T* __restrict__ out_t, float* __restrict__ out_f, int n_cols, int k) {
+  __shared__ float As[MG_M][MG_K + 1];
+  __shared__ float Bs[MG_N][MG_K + 1];
+  __shared__ float Us[MG_N][MG_K + 1];
+  __shared__ int pairs[MG_M];
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.x;
+  if (tile >= num_tiles[0]) return;
+  const bool gated = up_offset != 0;
+  const int tid = threadIdx.x;
+  if (tid < MG_M) pairs[tid] = sorted[tile * MG_M + tid];
+  __syncthreads();
+  const T* we = w + (int64_t)tile_expert[tile] * w_expert_stride;
+  const int col0 = blockIdx.y * MG_N;
+  const int ty = tid / 16, tx = tid % 16;          // rows 2 ty, 2 ty + 1; columns tx, tx + 16, tx + 32, tx + 48
+  float acc[2][4] = {}, acu[2][4] = {};
+  for (int k0 = 0; k0 < k; k0 += MG_K) {
+    for (int idx = tid; idx < MG_M * MG_K; idx += MG_THREADS) {
+      const int r = idx / MG_K, kk = idx % MG_K;
+      const int p = pairs[r];
+      As[r][kk] = (p >= 0 && k0 + kk < k) ? to_float(a[(int64_t)(p / a_div) * a_stride + k0 + kk]) : 0.f;
+    }
+    for (int idx = tid; idx < MG_N * MG_K; idx += MG_THREADS) {
+      const int c = idx / MG_K, kk = idx % MG_K;
+      const bool ok = col0 + c < n_cols && k0 + kk < k;
+      const int64_t at = (int64_t)(col0 + c) * k + k0 + kk;
+      Bs[c][kk] = ok ? to_float(we[at]) : 0.f;
+      if (gated) Us[c][kk] = ok ? to_float(we[up_offset + at]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < MG_K; ++kk) {
+      const float a0 = As[2 * ty][kk], a1 = As[2 * ty + 1][kk];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = Bs[tx + 16 * j][kk];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+        if (gated) {
+          const float u = Us[tx + 16 * j][kk];
+          acu[0][j] = fmaf(a0, u, acu[0][j]);
+          acu[1][j] = fmaf(a1, u, acu[1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int p = pairs[2 * ty + i];
+    if (p < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = col0 + tx + 16 * j;
+      if (c >= n_cols) continue;
+      if (gated) {
+        const float g = acc[i][j];
+        out_t[(int64_t)p * n_cols + c] = from_float<T>(g / (1.0f + expf(-g)) * acu[i][j]);
+      } else {
+        out_f[(int64_t)p * n_cols + c] = acc[i][j];
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const T* __restrict__ shared,
+                   T* __restrict__ out, int top, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < top; ++s) acc = fmaf(weights[t * top + s], y[(t * top + s) * width + c], acc);
+    if (shared) acc += to_float(shared[t * width + c]);
+    out[t * width + c] = from_float<T>(acc);
+  }
+}
+
+template <typename T>
+int moe_gemm_launch(const T* a, int64_t a_stride, int a_div, const T* w, int64_t w_expert_stride, int64_t up_offset,
+                    const int* sorted, const int* tile_expert, const int* num_tiles, void* out, int max_tiles,
+                    int n_cols, int k, int tile_m, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (tile_m != MG_M || n_cols < 1 || k < 1 || a_div < 1) return (int)cudaErrorInvalidValue;
+  const bool gated = up_offset != 0;
+  return gllm_launch(moe_gemm_kernel<T>, dim3(max_tiles, (n_cols + MG_N - 1) / MG_N), dim3(MG_THREADS), 0, stream, a,
+                     a_stride, a_div, w, w_expert_stride, up_offset, sorted, tile_expert, num_tiles,
+                     gated ? (T*)out : (T*)nullptr, gated ? (float*)nullptr : (float*)out, n_cols, k);
+}
+}  // namespace
+
+GLLM_API int gllm_moe_route(const float* logits, int64_t stride, const float* correction, int* ids, float* weights,
+                            int n_tokens, int experts, int top, int groups, int keep, int renorm, int reserved,
+                            cudaStream_t stream) {
+  (void)reserved;
+  if (n_tokens <= 0) return 0;
+  if (experts < 1 || top < 1 || top > experts || groups < 1 || experts % groups || keep < 1 || keep > groups ||
+      top > keep * (experts / groups))
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * (size_t)(2 * experts + groups);
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  return gllm_launch(moe_route_kernel, dim3(n_tokens), dim3(32), smem, stream, logits, stride, correction, ids, weights,
+                     experts, top, groups, keep, renorm);
+}
+
+GLLM_API int gllm_moe_align(const int* ids, int* sorted, int* tile_expert, int* num_tiles, int* reserved, int n_pairs,
+                            int experts, int tile_m, int max_tiles, cudaStream_t stream) {
+  (void)reserved;
+  if (n_pairs <= 0) return 0;
+  const size_t smem = sizeof(int) * (size_t)(3 * experts + 1);
+  if (smem > 48 * 1024 || tile_m < 1 || max_tiles < 1) return (int)cudaErrorInvalidValue;
+  return gllm_launch(moe_align_kernel, dim3(1), dim3(1024), smem, stream, ids, sorted, tile_expert, num_tiles, n_pairs,
+                     experts, tile_m, max_tiles);
+}
+
+GLLM_API int gllm_moe_gemm_f32(const float* a, int64_t a_stride, int a_div, const float* w, int64_t w_expert_stride,
+                               int64_t up_offset, const int* sorted, const int* tile_expert, const int* num_tiles,
+                               void* out, int max_tiles, int n_cols, int k, int tile_m, cudaStream_t stream) {
+  return moe_gemm_launch<float>(a, a_stride, a_div, w, w_expert_stride, up_offset, sorted, tile_expert, num_tiles, out,
+                                max_tiles, n_cols, k, tile_m, stream);
+}
+GLLM_API int gllm_moe_gemm_bf16(const __nv_bfloat16* a, int64_t a_stride, int a_div, const __nv_bfloat16* w,
+                                int64_t w_expert_stride, int64_t up_offset, const int* sorted, const int* tile_expert,
+                                const int* num_tiles, void* out, int max_tiles, int n_cols, int k, int tile_m,
+                                cudaStream_t stream) {
+  return moe_gemm_launch<__nv_bfloat16>(a, a_stride, a_div, w, w_expert_stride, up_offset, sorted, tile_expert,
+                                        num_tiles, out, max_tiles, n_cols, k, tile_m, stream);
+}
+
+GLLM_API int gllm_moe_combine_f32(const float* y, const float* weights, const float* shared, float* out, int n_tokens,
+                                  int top, int width, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  return gllm_launch(moe_combine_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, y, weights, shared, out, top,
+                     width);
+}
+GLLM_API int gllm_moe_combine_bf16(const float* y, const float* weights, const __nv_bfloat16* shared,
+                                   __nv_bfloat16* out, int n_tokens, int top, int width, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  return gllm_launch(moe_combine_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, y, weights, shared, out,
+                     top, width);
+}

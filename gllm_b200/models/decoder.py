@@ -157,7 +157,7 @@ class DecoderModel:
             resid = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row, scale=scale)
         branch = None
         first = None
-        if any(entry.rejoins_embedding for entry in self.spec.plan):
+        if any(entry.rejoins_embedding or entry.adds_embedding for entry in self.spec.plan):
             # the embedding output is kept: the residual itself is updated in place by the layers
             first = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row, scale=scale)
         for entry_idx, entry in enumerate(self.spec.plan):
@@ -165,6 +165,9 @@ class DecoderModel:
                 joined = ops.join_rows(None if branch is ops.ADDED else branch, resid, first, self.dtype)
                 resid = ops.linear(joined, self.rejoin, out_dtype=torch.float32)
                 branch = None
+            if entry.adds_embedding:
+                # the entry's first norm adds the embedding output together with the branch that is still pending
+                branch = ops.Pending.of(branch).with_extra(first)
             branch, resid = self.layers[entry.layer].forward(branch, resid, ctx, caches[entry_idx])
         if logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)

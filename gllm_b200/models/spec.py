@@ -63,6 +63,9 @@ class PlanEntry:
     # stands, ``x0`` the embedding output and ``W`` the model's ``rejoin_name`` tensor ``[hidden, 2 * hidden]``
     # (a stretch of layers that is run several times re-reads the embedding at the start of each pass).
     rejoins_embedding: bool = False
+    # True: before this entry runs, the embedding output is added to the residual (a further pass of a repeated
+    # stretch takes the embedding in again); the add happens inside the entry's first norm kernel.
+    adds_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -104,6 +107,9 @@ class ModelSpec:
                 raise ValueError(f"plan entry {i} rejoins the embedding, but the model names no matrix for that")
             if entry.rejoins_embedding and self.residual_streams != 1:
                 raise ValueError("rejoining the embedding is defined for a single residual stream")
+            if entry.adds_embedding and (self.residual_streams != 1 or entry.rejoins_embedding):
+                raise ValueError("adding the embedding output is defined for a single residual stream, and an entry "
+                                 "either adds it or rejoins it")
             if entry.reads_cache_of is not None:
                 j = entry.reads_cache_of
                 if not 0 <= j < i:

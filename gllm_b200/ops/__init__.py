@@ -47,6 +47,8 @@ __all__ = [
     "residual_add",
     "join_rows",
     "qk_rownorm",
+    "Pending",
+    "rope_norm_store",
 ]
 
 P = c_void_p
@@ -101,6 +103,24 @@ _SIGNATURES = {
         "gllm_head_linear_{t}": [P, c_int64, c_int, P, P, c_int64, c_int, c_int, c_int, c_int, c_int, P],
         "gllm_attention_latent_{t}": [P, c_int64, c_int, P, c_int64, c_int, P, c_int64, P, c_int64, c_int, P, P, c_int,
                                       P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P],
+    },
+    "postnorm": {
+        "gllm_postnorm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, c_float, P, P, P, c_float, P, P, c_int, c_int, P],
+    },
+    "rope_norm": {
+        "gllm_rope_norm_store_{t}": [P, P, c_int, c_int64, P, P, c_float, P, P, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, c_float, c_int, c_int, P, P],
+    },
+    "delta_rule": {
+        "gllm_delta_prep_{t}": [P, c_int64, P, P, P, P, P, P, c_int, P, c_int64, P, P, P, c_int64, P, P, P, P, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_float, c_float, P],
+        "gllm_delta_rule": [P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    },
+    "moe": {
+        "gllm_moe_route": [P, c_int64, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
+        "gllm_moe_align": [P, P, P, P, P, c_int, c_int, c_int, c_int, P],
+        "gllm_moe_gemm_{t}": [P, c_int64, c_int, P, c_int64, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, P],
+        "gllm_moe_combine_{t}": [P, P, P, P, c_int, c_int, c_int, P],
     },
     "attention_simt": {
         "gllm_attention_simt_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
@@ -309,6 +329,29 @@ def as_tensor(x):
     return x.tensor() if isinstance(x, SplitSum) else x
 
 
+class Pending:
+    """What is still to be added to the fp32 residual stream when the next norm runs: ``value`` (a tensor of the
+    activation type, a SplitSum, or None), first RMS-normed with ``post_weight`` and ``post_eps`` when a weight is
+    given (a layer that norms a sublayer's result before it joins the residual), and ``extra``: a second fp32
+    stream of the residual's shape that is added as it is.  ``add_rmsnorm`` does all of it in one kernel."""
+
+    def __init__(self, value=None, post_weight: torch.Tensor | None = None, post_eps: float = 0.0,
+                 extra: torch.Tensor | None = None):
+        self.value, self.post_weight, self.post_eps, self.extra = value, post_weight, float(post_eps), extra
+
+    @classmethod
+    def of(cls, branch) -> "Pending":
+        """``branch`` as a Pending: itself, or a plain add of a tensor / SplitSum (nothing for None and ADDED)."""
+        if isinstance(branch, Pending):
+            return branch
+        return cls(None if branch is None or branch is ADDED else branch)
+
+    def with_extra(self, extra: torch.Tensor) -> "Pending":
+        if self.extra is not None:
+            raise ValueError("a second stream is already pending")
+        return Pending(self.value, self.post_weight, self.post_eps, extra)
+
+
 def _parts_args(x):
     if isinstance(x, SplitSum):
         x.check_alive()
@@ -415,6 +458,13 @@ def add_rmsnorm(
     hidden = resid.shape[-1]
     if weight.numel() != hidden:
         raise ValueError(f"norm weight has {weight.numel()} elements, rows have {hidden}")
+    if isinstance(branch, Pending):
+        if branch.post_weight is None and branch.extra is None:
+            branch = branch.value
+        else:
+            if unit_offset:
+                raise ValueError("a norm whose weight is stored around zero does not take a pending normed branch")
+            return _pending_add_rmsnorm(branch, resid, weight, eps, out_dtype, rows, out)
     parts_ptr, n_parts, part_stride = _parts_args(branch)
     if isinstance(branch, SplitSum):
         if tuple(branch.shape) != tuple(resid.shape) or branch.dtype != out_dtype:
@@ -436,6 +486,41 @@ def add_rmsnorm(
     f = _fn("elementwise", f"gllm_add_rmsnorm_{_suffix(out_dtype)}")
     _check(f(_ptr(branch), parts_ptr, n_parts, part_stride, resid.data_ptr(), weight.data_ptr(), out.data_ptr(),
              _ptr(rows), n_rows, hidden, float(eps), int(unit_offset), _stream()), "add_rmsnorm")
+    return out
+
+
+def _pending_add_rmsnorm(pending: Pending, resid, weight, eps, out_dtype, rows, out):
+    """``resid += rms(value) * post_weight + extra`` and the RMS norm of the sum (``csrc/postnorm.cu``)."""
+    n_total, hidden = resid.numel() // resid.shape[-1], resid.shape[-1]
+    value = pending.value
+    parts_ptr, n_parts, part_stride = _parts_args(value)
+    if isinstance(value, SplitSum):
+        if tuple(value.shape) != tuple(resid.shape) or value.dtype != out_dtype:
+            raise ValueError("the pending value and the residual differ in shape or dtype")
+        value = None
+    elif value is not None:
+        _cuda(value, "value", out_dtype)
+        if value.shape != resid.shape:
+            raise ValueError("the pending value and the residual differ in shape")
+    if pending.post_weight is not None:
+        _cuda(pending.post_weight, "post_weight", torch.float32)
+        if pending.post_weight.numel() != hidden:
+            raise ValueError("the post-norm weight needs one value per column")
+    if pending.extra is not None:
+        _cuda(pending.extra, "extra", torch.float32)
+        if pending.extra.shape != resid.shape:
+            raise ValueError("the second stream and the residual differ in shape")
+    n_rows = n_total if rows is None else rows.numel()
+    if rows is not None:
+        _cuda(rows, "rows", torch.int32)
+    if out is None:
+        out = torch.empty((n_rows, hidden), dtype=out_dtype, device=resid.device)
+    else:
+        _cuda(out, "out", out_dtype)
+    f = _fn("postnorm", f"gllm_postnorm_add_rmsnorm_{_suffix(out_dtype)}")
+    _check(f(_ptr(value), parts_ptr, n_parts, part_stride, _ptr(pending.post_weight), pending.post_eps,
+             _ptr(pending.extra), resid.data_ptr(), weight.data_ptr(), float(eps), out.data_ptr(), _ptr(rows), n_rows,
+             hidden, _stream()), "postnorm_add_rmsnorm")
     return out
 
 
@@ -644,6 +729,40 @@ def rope_store(
              _ptr(slot_mapping), _ptr(cache_layer) if slot_mapping is not None else None, n, num_heads,
              num_kv_heads, head_dim, rotary_dim, int(interleaved), block_size, num_pages,
              status_word(qkv.device).data_ptr(), _stream()), "rope_store")
+    return qkv
+
+
+def rope_norm_store(qkv, positions: torch.Tensor, inv_freq: torch.Tensor | None, magnitude: float,
+                    slot_mapping: torch.Tensor | None, cache_layer: torch.Tensor | None, num_heads: int,
+                    num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool, norm_dim: int,
+                    eps: float) -> torch.Tensor:
+    """As ``rope_store`` for layers whose sine and cosine are multiplied by ``magnitude`` and whose query and key
+    heads are divided, AFTER the rotation, by ``sqrt(sum(x^2) / norm_dim + eps)`` (``norm_dim`` 0: no norm; it may
+    be smaller than ``head_dim`` when heads are stored with zero columns behind them).  Returns ``qkv``."""
+    parts_ptr, n_parts, part_stride = _parts_args(qkv)
+    if isinstance(qkv, SplitSum):
+        qkv = torch.empty(tuple(qkv.shape), dtype=qkv.dtype, device=qkv.device)
+    _cuda(qkv, "qkv")
+    _cuda(positions, "positions", torch.int32)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise ValueError("qkv width does not equal (heads + 2*kv_heads) * head_dim")
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise ValueError("inv_freq must hold rotary_dim/2 frequencies")
+    block_size = num_pages = 0
+    if slot_mapping is not None:
+        _cuda(slot_mapping, "slot_mapping", torch.int32)
+        _cuda(cache_layer, "cache_layer", qkv.dtype)
+        num_pages, two, hkv, block_size, d = cache_layer.shape
+        if two != 2 or hkv != num_kv_heads or d != head_dim:
+            raise ValueError("cache layer shape does not match the mixer's heads")
+    f = _fn("rope_norm", f"gllm_rope_norm_store_{_suffix(qkv.dtype)}")
+    _check(f(qkv.data_ptr(), parts_ptr, n_parts, part_stride, positions.data_ptr(), _ptr(inv_freq), float(magnitude),
+             _ptr(slot_mapping), _ptr(cache_layer) if slot_mapping is not None else None, n, num_heads, num_kv_heads,
+             head_dim, rotary_dim if inv_freq is not None else 0, int(interleaved), int(norm_dim), float(eps),
+             block_size, num_pages, status_word(qkv.device).data_ptr(), _stream()), "rope_norm_store")
     return qkv
 
 

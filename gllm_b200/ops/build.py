@@ -54,6 +54,10 @@ MODULES = {
     "attention_sigmoid_mma": "attention_sigmoid_mma.cu",
     "attention_latent": "attention_latent.cu",
     "attention_latent_mma": "attention_latent_mma.cu",
+    "postnorm": "postnorm.cu",
+    "rope_norm": "rope_norm.cu",
+    "delta_rule": "delta_rule.cu",
+    "moe": "moe.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,87 @@
+"""Python entry points of the routed-expert kernels (``csrc/moe.cu``).  As everywhere in ``gllm_b200.ops``: CUDA
+tensors only, no CPU path; everything that varies between steps of equal shape (which experts were chosen, how
+many tiles they fill) stays on the device, so a step can be captured in a CUDA graph."""
+
+from __future__ import annotations
+
+import torch
+
+from gllm_b200.ops import _check, _cuda, _fn, _ptr, _stream, _suffix
+
+TILE_ROWS = 16        # rows of one tile of the expert products: an expert's pairs are padded to a multiple of it
+
+
+def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int = 1, groups_kept: int = 1,
+          renormalize: bool = False):
+    """From fp32 router logits ``[n, experts]`` to the chosen experts ``[n, top]`` int32 and their weights fp32.
+    Scores ``s = sigmoid(logits)``; the choice is made on ``s + correction`` among the experts of the
+    ``groups_kept`` best of ``groups`` equal groups of neighbours (a group's score: the sum of its two largest
+    choice scores); the weights are the chosen ``s``, divided by their sum with ``renormalize``."""
+    _cuda(logits, "logits", torch.float32, contiguous=False)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("router logits must be [tokens, experts] with contiguous columns")
+    if correction is not None:
+        _cuda(correction, "correction", torch.float32)
+        if correction.numel() != logits.shape[1]:
+            raise ValueError("one correction value per expert is needed")
+    n, experts = logits.shape
+    ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    _check(_fn("moe", "gllm_moe_route")(logits.data_ptr(), logits.stride(0), _ptr(correction), ids.data_ptr(),
+                                        weights.data_ptr(), n, experts, int(top), int(groups), int(groups_kept),
+                                        int(renormalize), 0, _stream()), "moe_route")
+    return ids, weights
+
+
+def align(ids: torch.Tensor, experts: int):
+    """The (token, slot) pairs sorted by expert in tiles of ``TILE_ROWS`` rows: ``(sorted [max_tiles * TILE_ROWS]``
+    (pair index or -1), ``tile_expert [max_tiles]``, ``num_tiles [1])``, all int32 on the device."""
+    _cuda(ids, "ids", torch.int32)
+    pairs = ids.numel()
+    max_tiles = -(-pairs // TILE_ROWS) + min(experts, pairs)
+    sorted_pairs = torch.empty(max_tiles * TILE_ROWS, dtype=torch.int32, device=ids.device)
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=ids.device)
+    num_tiles = torch.empty(1, dtype=torch.int32, device=ids.device)
+    _check(_fn("moe", "gllm_moe_align")(ids.data_ptr(), sorted_pairs.data_ptr(), tile_expert.data_ptr(),
+                                        num_tiles.data_ptr(), None, pairs, int(experts), TILE_ROWS, max_tiles,
+                                        _stream()), "moe_align")
+    return sorted_pairs, tile_expert, num_tiles
+
+
+def expert_product(a: torch.Tensor, rows_per_input: int, weight: torch.Tensor, plan, n_pairs: int, gated: bool):
+    """``out[pair] = a[pair // rows_per_input] @ weight[expert of pair].T`` for the pairs of ``plan`` (what
+    ``align`` returned).  ``weight [experts, rows, k]``; ``gated``: its rows are gate rows then up rows and the
+    result is ``silu(gate) * up`` in the activation type ``[n_pairs, rows / 2]``; otherwise fp32 ``[n_pairs, rows]``."""
+    _cuda(a, "a", contiguous=False)
+    _cuda(weight, "weight", a.dtype)
+    if a.dim() != 2 or a.stride(1) != 1 or weight.dim() != 3 or weight.shape[2] != a.shape[1]:
+        raise ValueError("the expert product takes rows of contiguous columns and weights [experts, rows, k]")
+    sorted_pairs, tile_expert, num_tiles = plan
+    rows, k = weight.shape[1], weight.shape[2]
+    if gated and rows % 2:
+        raise ValueError("gate and up rows come in equal numbers")
+    n_cols = rows // 2 if gated else rows
+    out = torch.empty((n_pairs, n_cols), dtype=a.dtype if gated else torch.float32, device=a.device)
+    f = _fn("moe", f"gllm_moe_gemm_{_suffix(a.dtype)}")
+    _check(f(a.data_ptr(), a.stride(0), int(rows_per_input), weight.data_ptr(), weight.stride(0),
+             n_cols * k if gated else 0, sorted_pairs.data_ptr(), tile_expert.data_ptr(), num_tiles.data_ptr(),
+             out.data_ptr(), tile_expert.numel(), n_cols, k, TILE_ROWS, _stream()), "moe_gemm")
+    return out
+
+
+def combine(y: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
+    """``out[t] = sum_s weights[t, s] * y[t * top + s] (+ shared[t])``, summed in slot order in fp32."""
+    _cuda(y, "y", torch.float32)
+    _cuda(weights, "weights", torch.float32)
+    n, top = weights.shape
+    width = y.shape[1]
+    if y.shape[0] != n * top:
+        raise ValueError("one result row per (token, slot) pair is needed")
+    if shared is not None:
+        _cuda(shared, "shared", out_dtype)
+        if tuple(shared.shape) != (n, width):
+            raise ValueError("the shared expert's result does not fit")
+    out = torch.empty((n, width), dtype=out_dtype, device=y.device)
+    _check(_fn("moe", f"gllm_moe_combine_{_suffix(out_dtype)}")(y.data_ptr(), weights.data_ptr(), _ptr(shared),
+                                                               out.data_ptr(), n, top, width, _stream()), "moe_combine")
+    return out

@@ -222,6 +222,67 @@ def head_norm(o: torch.Tensor, heads: int, dv: int, weight: torch.Tensor, eps: f
     return out
 
 
+# ------------------------------------------------------------------ gated delta rule
+def delta_prep(x: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Tensor, positions: torch.Tensor,
+               token_row: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, num_requests: int,
+               decay_raw: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, beta_raw: torch.Tensor, heads: int,
+               kv_heads: int, dk: int, dv: int, unit_eps: float, q_scale: float):
+    """What the delta rule's recurrence takes, in fp32, from the projections of a step's tokens.
+
+    ``x [n, >= channels]`` (rows may be slices): the q | k | v projections, ``channels = 2 * kv_heads * dk +
+    heads * dv``; each channel passes a causal convolution over the request's own tokens (``conv_weight
+    [channels, taps]`` fp32, last column = the current token; ``conv_state [slots, taps-1, channels]`` fp32 holds
+    every request's last inputs, oldest first, and is brought up to date) and SiLU; every q and k head becomes
+    ``x / sqrt(sum(x^2) + unit_eps)``, q also times ``q_scale``.  ``decay_raw [n, heads * dk]`` and ``beta_raw
+    [n, heads]`` are fp32: ``g = exp(-exp(A_log[h]) * softplus(decay_raw + dt_bias))``, ``beta = sigmoid(beta_raw)``.
+    Returns ``(qk [n, 2 * kv_heads * dk], v [n, heads * dv], g [n, heads * dk], beta [n, heads])``."""
+    _rows(x, "x")
+    _rows(decay_raw, "decay_raw", torch.float32)
+    _rows(beta_raw, "beta_raw", torch.float32)
+    for name, t in (("conv_weight", conv_weight), ("conv_state", conv_state), ("dt_bias", dt_bias), ("A_log", A_log)):
+        _cuda(t, name, torch.float32)
+    n = x.shape[0]
+    qk_cols, channels = 2 * kv_heads * dk, 2 * kv_heads * dk + heads * dv
+    taps = conv_weight.shape[1]
+    if (x.shape[1] < channels or conv_weight.shape[0] != channels
+            or tuple(conv_state.shape[1:]) != (max(taps - 1, 0), channels) or decay_raw.shape[1] != heads * dk
+            or beta_raw.shape[1] != heads or dt_bias.numel() != heads * dk or A_log.numel() != heads):
+        raise ValueError("the delta rule's operands do not fit together")
+    dev = x.device
+    qk = torch.empty((n, qk_cols), dtype=torch.float32, device=dev)
+    v = torch.empty((n, heads * dv), dtype=torch.float32, device=dev)
+    g = torch.empty((n, heads * dk), dtype=torch.float32, device=dev)
+    beta = torch.empty((n, heads), dtype=torch.float32, device=dev)
+    f = _fn("delta_rule", f"gllm_delta_prep_{_suffix(x.dtype)}")
+    _check(f(x.data_ptr(), x.stride(0), conv_weight.data_ptr(), conv_state.data_ptr(), positions.data_ptr(),
+             token_row.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(), int(num_requests), decay_raw.data_ptr(),
+             decay_raw.stride(0), dt_bias.data_ptr(), A_log.data_ptr(), beta_raw.data_ptr(), beta_raw.stride(0),
+             qk.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), n, heads, kv_heads, dk, dv, taps,
+             float(unit_eps), float(q_scale), _stream()), "delta_prep")
+    return qk, v, g, beta
+
+
+def delta_rule(qk: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+               cu_q: torch.Tensor, state_slots: torch.Tensor, num_requests: int, heads: int, kv_heads: int, dk: int,
+               dv: int, max_q_len: int = 0) -> torch.Tensor:
+    """Per (request, head), token after token: ``S <- diag(g) S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``,
+    ``o = S^T q`` (the read-out sees the token's own write).  Operands as ``delta_prep`` returns them; head ``h``
+    uses the q and k of head ``h // (heads / kv_heads)``.  ``state [slots, heads, dv, dk]`` fp32 (one row per value
+    column) is updated in place.  Returns fp32 ``[n, heads * dv]``."""
+    for name, t in (("qk", qk), ("v", v), ("g", g), ("beta", beta), ("state", state)):
+        _cuda(t, name, torch.float32)
+    n = qk.shape[0]
+    if (tuple(state.shape[1:]) != (heads, dv, dk) or qk.shape[1] != 2 * kv_heads * dk or v.shape[1] != heads * dv
+            or g.shape[1] != heads * dk or beta.shape[1] != heads):
+        raise ValueError("the delta rule's operands do not fit together")
+    out = torch.empty((n, heads * dv), dtype=torch.float32, device=qk.device)
+    f = _fn("delta_rule", "gllm_delta_rule")
+    _check(f(qk.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), state.data_ptr(), cu_q.data_ptr(),
+             state_slots.data_ptr(), out.data_ptr(), int(num_requests), heads, kv_heads, dk, dv, int(max_q_len),
+             _stream()), "delta_rule")
+    return out
+
+
 # ------------------------------------------------------------------ sigmoid attention
 def qk_norm_store(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, eps: float, temp_coef: float,
                   temp_every: float, positions: torch.Tensor, slot_mapping: torch.Tensor | None,

@@ -37,6 +37,7 @@ class TensorExpectation:
     in fp32 whatever the compute dtype is.  "bias": the bias of a projection, held in fp32
     as well (random weights draw it around zero, a vector around one).  "mixing": a small square matrix
     that mixes parallel streams, fp32 (random weights draw it around the identity).  "int_table": integer table, int32.
+    A size of -1 in ``shape`` is one that only the checkpoint gives (the part reads it when it loads).
     """
 
     shape: tuple[int, ...]

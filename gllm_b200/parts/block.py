@@ -53,3 +53,26 @@ class SharedNormBlock(Block):
             out = self.feed_forward.forward(x, ctx)
         ctx.residual_sink = None
         return out, resid
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """A norm before and a norm after each sublayer: ``x += post_a(mixer(pre_a(x))); x += post_b(ff(pre_b(x)))``.
+    A sublayer's result is not normed and added by a kernel of its own: it travels on as ``ops.Pending`` (the
+    result with the post-norm's weight) and the NEXT pre-norm's kernel does the post-norm, the add and its own
+    norm in one pass, as the pre-norm block defers its plain adds.  The sublayers' last products cannot add
+    themselves into the residual (their result is normed first).  A layer may have no feed-forward."""
+
+    graph_safe_portions = True
+    part_kinds = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
+                  "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+    optional_parts = frozenset({"feed_forward_norm", "feed_forward", "feed_forward_post_norm"})
+
+    def forward(self, branch, resid, ctx, cache):
+        ctx.residual_sink = None
+        x = self.mixer_norm.forward(None if branch is ops.ADDED else branch, resid, ctx.dtype)
+        out = self.mixer_post_norm.pending(self.mixer.forward(x, ctx, cache))
+        if self.feed_forward is not None:
+            x = self.feed_forward_norm.forward(out, resid, ctx.dtype)
+            out = self.feed_forward_post_norm.pending(self.feed_forward.forward(x, ctx))
+        return out, resid

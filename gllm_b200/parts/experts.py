@@ -1,0 +1,91 @@
+"""Routed experts: every token is served by ``top`` of ``experts`` small gated feed-forwards
+``down(silu(gate(x)) * up(x))`` (no biases), optionally beside a shared expert that serves every token.
+
+Router logits ``z = W_router x`` in fp32; scores ``s = sigmoid(z)``.  The choice is made on ``s + correction``
+(a stored vector that steers the choice only), with ``groups``: only among the experts of the ``groups_kept``
+best of ``groups`` equal groups of neighbouring experts, a group's score being the sum of its two largest choice
+scores.  The result is ``sum_e s_e * expert_e(x)`` over the chosen experts (weights divided by their sum with
+``renormalize``) plus the shared expert's.  The (token, expert) pairs are sorted by expert on the device and the
+experts' products run over tiles of one expert each (``csrc/moe.cu``); nothing about the choice reaches the host.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from gllm_b200 import ops
+from gllm_b200.ops import moe
+from gllm_b200.parts.base import FEED_FORWARDS, FeedForward, TensorExpectation, build_part, register_feed_forward
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    graph_safe_portions = True
+
+    def __init__(self, names, hidden_size: int, intermediate_size: int, experts: int, top: int,
+                 groups: int | None = None, groups_kept: int | None = None, score: str = "sigmoid",
+                 renormalize: bool = False, correction: bool = False, shared=None):
+        """``names``: ``router``, ``correction`` (with ``correction``) and ``expert``, a pattern with ``{index}`` and
+        ``{part}`` (gate | up | down).  ``shared``: the PartSpec of a feed-forward that runs for every token."""
+        super().__init__(names)
+        if score != "sigmoid":
+            raise ValueError(f"unknown router score {score!r}; known: ['sigmoid']")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.experts, self.top = int(experts), int(top)
+        self.groups = int(groups) if groups else 1
+        self.groups_kept = int(groups_kept) if groups else 1
+        if (self.experts % self.groups or not 1 <= self.groups_kept <= self.groups
+                or not 1 <= self.top <= self.groups_kept * (self.experts // self.groups)):
+            raise ValueError("the experts form equal groups, and 'top' experts must be left to choose from")
+        self.renormalize, self.has_correction = bool(renormalize), bool(correction)
+        self.shared = build_part(FEED_FORWARDS, shared) if shared is not None else None
+        self.w_router = self.correction = self.w_gate_up = self.w_down = None
+
+    def kernel_needs(self):
+        needs = {"modules": {"moe"}}
+        if self.shared is not None:
+            for key, values in self.shared.kernel_needs().items():
+                needs.setdefault(key, set()).update(values)
+        return needs
+
+    def _expert(self, index: int, part: str) -> str:
+        return self.names["expert"].format(index=index, part=part)
+
+    def expected_tensors(self):
+        h, i = self.hidden_size, self.intermediate_size
+        exp = {self.names["router"]: TensorExpectation((self.experts, h))}
+        if self.has_correction:
+            exp[self.names["correction"]] = TensorExpectation((self.experts,), "bias")
+        for e in range(self.experts):
+            exp[self._expert(e, "gate")] = TensorExpectation((i, h))
+            exp[self._expert(e, "up")] = TensorExpectation((i, h))
+            exp[self._expert(e, "down")] = TensorExpectation((h, i))
+        if self.shared is not None:
+            exp.update(self.shared.expected_tensors())
+        return exp
+
+    def load(self, get, dtype, device):
+        self.w_router = get(self.names["router"], "matrix").contiguous()
+        if self.has_correction:
+            self.correction = get(self.names["correction"], "bias").contiguous()
+        # [experts, 2 * ff, width]: an expert's gate rows, then its up rows; [experts, width, ff]
+        self.w_gate_up = torch.stack([torch.cat([get(self._expert(e, "gate"), "matrix"),
+                                                 get(self._expert(e, "up"), "matrix")], 0)
+                                      for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([get(self._expert(e, "down"), "matrix") for e in range(self.experts)]).contiguous()
+        if self.shared is not None:
+            self.shared.load(get, dtype, device)
+
+    def forward(self, x, ctx):
+        logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
+        ids, weights = moe.route(logits, self.correction, self.top, self.groups, self.groups_kept, self.renormalize)
+        plan = moe.align(ids, self.experts)
+        pairs = ids.numel()
+        hidden = moe.expert_product(x, self.top, self.w_gate_up, plan, pairs, gated=True)
+        y = moe.expert_product(hidden, 1, self.w_down, plan, pairs, gated=False)
+        shared = None
+        if self.shared is not None:
+            sink, ctx.residual_sink = getattr(ctx, "residual_sink", None), None
+            shared = ops.as_tensor(self.shared.forward(x, ctx))
+            ctx.residual_sink = sink
+        return moe.combine(y, weights, shared, x.dtype)

@@ -33,5 +33,12 @@ class RMSNorm(Norm):
     def load(self, get, dtype, device):
         self.weight = get(self.names["weight"], "vector")
 
+    def pending(self, value):
+        """``value`` (a sublayer's result) as what the NEXT norm's kernel norms with this norm's weight and adds
+        to the residual: the norm after a sublayer of a layer that norms both sides of it."""
+        if self.unit_offset:
+            raise ValueError("a norm whose weight is stored around zero cannot follow a sublayer")
+        return ops.Pending(None if value is ops.ADDED else value, self.weight, self.eps)
+
     def forward(self, branch, resid, dtype, rows=None):
         return ops.add_rmsnorm(branch, resid, self.weight, self.eps, dtype, rows=rows, unit_offset=self.unit_offset)

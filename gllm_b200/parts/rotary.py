@@ -1,4 +1,4 @@
-"""Rotary position encoding with optional llama3 frequency scaling.
+"""Rotary position encoding with optional llama3 or yarn frequency scaling.
 
 Frequencies ``theta ** (-2m / rotary_dim)`` for m = 0 .. rotary_dim/2 - 1 as
 gllm/model/model.py:119-123; each head's first ``rotary_dim`` dims are rotated
@@ -23,12 +23,29 @@ def scaled_inverse_frequencies(
     theta: float,
     scaling: dict | None = None,
 ) -> list[float]:
-    """Float64 frequencies, llama3-scaled when ``scaling`` says so."""
+    """Float64 frequencies, scaled as ``scaling["rope_type"]`` says ("llama3" or "yarn")."""
     half = rotary_dim // 2
     freqs = [float(theta) ** (-2.0 * m / rotary_dim) for m in range(half)]
     if not scaling:
         return freqs
     kind = scaling.get("rope_type")
+    if kind == "yarn":
+        # Pair m keeps its frequency below pair ``lo`` and has it divided by ``factor`` from pair ``hi`` on, with a
+        # linear ramp between; lo and hi are the pairs that make ``beta_fast`` and ``beta_slow`` turns over the
+        # original context: pair(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta).
+        factor = float(scaling["factor"])
+        original = float(scaling["original_max_position_embeddings"])
+
+        def pair_of(turns: float) -> float:
+            return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+
+        lo = max(math.floor(pair_of(float(scaling["beta_fast"]))), 0)
+        hi = min(math.ceil(pair_of(float(scaling["beta_slow"]))), rotary_dim - 1)
+        out = []
+        for m, f in enumerate(freqs):
+            ramp = min(max((m - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / factor * ramp + f * (1.0 - ramp))
+        return out
     if kind != "llama3":
         raise ValueError(f"rotary scaling {kind!r} is not supported")
     factor = float(scaling["factor"])
@@ -46,6 +63,13 @@ def scaled_inverse_frequencies(
             smooth = (original / wavelength - low) / (high - low)
             out.append((1.0 - smooth) * f / factor + smooth * f)
     return out
+
+
+def rotary_magnitude(scaling: dict | None) -> float:
+    """What sine and cosine are multiplied by: ``0.1 ln(factor) + 1`` under yarn scaling, 1 otherwise."""
+    if scaling and scaling.get("rope_type") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 @register_position_encoding("rotary")
@@ -70,6 +94,10 @@ class RotaryEncoding(PositionEncoding):
 
     def rotary(self):
         return self.inv_freq, self.rotary_dim, self.interleaved
+
+    def magnitude(self) -> float:
+        """The multiplier of sine and cosine (1 unless the scaling kind has one)."""
+        return rotary_magnitude(self.scaling)
 
 
 @register_position_encoding("none")

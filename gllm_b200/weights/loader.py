@@ -29,6 +29,11 @@ class WeightError(ValueError):
     """The checkpoint does not hold what the model expects."""
 
 
+def _shape_fits(found: tuple[int, ...], expected: tuple[int, ...]) -> bool:
+    """An expected size of -1 stands for a size that only the checkpoint gives (a low rank, say)."""
+    return len(found) == len(expected) and all(e == -1 or f == e for f, e in zip(found, expected))
+
+
 class Checkpoint:
     """Lazy view of all ``*.safetensors`` files of a folder."""
 
@@ -77,7 +82,7 @@ class Checkpoint:
         wrong = [
             (n, self._shapes[n], tuple(e.shape))
             for n, e in sorted(expected.items())
-            if n in self._where and self._shapes[n] != tuple(e.shape)
+            if n in self._where and not _shape_fits(self._shapes[n], tuple(e.shape))
         ]
         if not (missing or unexpected or wrong):
             return

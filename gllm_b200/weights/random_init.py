@@ -42,6 +42,8 @@ def random_tensors(
     dtype = _TORCH_DTYPES[config.dtype]
     out: dict[str, torch.Tensor] = {}
     for name, exp in expected_tensors_of(config).items():
+        if any(d < 0 for d in exp.shape):
+            raise ValueError(f"the shape of {name} has a size that only a checkpoint gives: name it in the configuration")
         if exp.role == "vector":
             t = torch.ones(exp.shape, dtype=torch.float32)
             if norm_jitter:
