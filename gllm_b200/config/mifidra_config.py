@@ -7,7 +7,9 @@ delta rule, ``left_scale``, ``right_scale``) and ``mlp`` (``{"kind": "dense", "f
 or null for a layer without a feed-forward), and optionally ``loop`` (``start``, ``stop``, ``times``: layers
 ``start .. stop-1`` run ``times`` times in a row with the same weights).  Every size and constant the model uses
 comes from here or from a tensor's shape; what a key that may be absent would switch on is off without it
-(``rot.scaling``, ``router.groups``, ``mlp.shared``, ``loop``).
+(``rot.scaling``, ``router.groups``, ``mlp.shared``, ``loop``).  ``right`` may also name ``decay_rank`` and
+``gate_rank``, the inner sizes of its two low-rank projections: a checkpoint's tensors give them, only the
+random-weights mode needs them named.
 """
 
 from __future__ import annotations

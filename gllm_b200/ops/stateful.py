@@ -229,7 +229,7 @@ def delta_prep(x: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Ten
                kv_heads: int, dk: int, dv: int, unit_eps: float, q_scale: float):
     """What the delta rule's recurrence takes, in fp32, from the projections of a step's tokens.
 
-    ``x [n, >= channels]`` (rows may be slices): the q | k | v projections, ``channels = 2 * kv_heads * dk +
+    ``x [n, >= channels]`` (rows may be slices): the q | k | v projections (``token_row``: each token's state slot), ``channels = 2 * kv_heads * dk +
     heads * dv``; each channel passes a causal convolution over the request's own tokens (``conv_weight
     [channels, taps]`` fp32, last column = the current token; ``conv_state [slots, taps-1, channels]`` fp32 holds
     every request's last inputs, oldest first, and is brought up to date) and SiLU; every q and k head becomes

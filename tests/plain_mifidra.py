@@ -157,8 +157,10 @@ def glu(h, w, pre, bias):
     return y + w[pre + ".down.b"] if bias else y
 
 
-def route(h, w, pre, router):
-    """Chosen experts ``[T, top]`` and their weights (the uncorrected sigmoid scores, not renormalised)."""
+def route(h, w, pre, router, margins: list | None = None):
+    """Chosen experts ``[T, top]`` and their weights (the uncorrected sigmoid scores, not renormalised).
+    ``margins`` collects the smallest gap between what was just chosen and what was just not (groups and
+    experts): a test whose gap is small rests on rounding."""
     E, top = int(router["experts"]), int(router["top"])
     s = torch.sigmoid(h @ w[pre + ".router"].T)
     choice = s + w[pre + ".correction"]
@@ -168,14 +170,20 @@ def route(h, w, pre, router):
         per = choice.view(-1, count, E // count)
         score = per.topk(min(2, E // count), -1).values.sum(-1)
         best = score.topk(keep, -1).indices
+        if margins is not None and keep < count:
+            ranked = score.sort(-1, descending=True).values
+            margins.append(float((ranked[:, keep - 1] - ranked[:, keep]).min()))
         allowed = torch.zeros_like(score, dtype=torch.bool).scatter_(1, best, True)
         choice = per.masked_fill(~allowed[:, :, None], float("-inf")).reshape(-1, E)
     chosen = choice.topk(top, -1).indices
+    if margins is not None and top < E:
+        ranked = choice.sort(-1, descending=True).values
+        margins.append(float((ranked[:, top - 1] - ranked[:, top]).min()))
     return chosen, s.gather(1, chosen)
 
 
-def moe(h, w, pre, mlp):
-    chosen, weights = route(h, w, pre, mlp["router"])
+def moe(h, w, pre, mlp, margins: list | None = None):
+    chosen, weights = route(h, w, pre, mlp["router"], margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(chosen[t].tolist(), weights[t]):
@@ -211,8 +219,12 @@ class PlainState:
         self.length = 0
 
 
-def forward(cfg, weights, tokens, state: PlainState | None = None, layers_out: list | None = None):
-    """Logits ``[T, vocab]`` (float64) of ``tokens`` continuing ``state`` (a fresh one if None)."""
+def forward(cfg, weights, tokens, state: PlainState | None = None, layers_out: list | None = None,
+            margins: list | None = None, stored: torch.dtype | None = None):
+    """Logits ``[T, vocab]`` (float64) of ``tokens`` continuing ``state`` (a fresh one if None).  ``stored``: what
+    the sublayers read and what they return is rounded to this type (the arithmetic stays float64): how far the
+    logits at a position move then says how much rounding alone matters there."""
+    keep = (lambda t: t.to(stored).to(F)) if stored is not None else (lambda t: t)
     w = {k: v.to(F) for k, v in weights.items()}
     eps = float(cfg["norm"]["eps"])
     state = state or PlainState(cfg)
@@ -225,7 +237,7 @@ def forward(cfg, weights, tokens, state: PlainState | None = None, layers_out: l
         layer, pre = cfg["layers"][i], f"l{i}"
         if add_embedding:
             x = x + x0
-        h = rms_norm(x, w[pre + ".norm1"], eps)
+        h = keep(rms_norm(x, w[pre + ".norm1"], eps))
         m = layer["mixer"]
         q, k, v = left_project(h, p, m["left"], w, pre + ".mix.left", eps)
         state.k[run] = k if state.k[run] is None else torch.cat([state.k[run], k], 0)
@@ -233,12 +245,12 @@ def forward(cfg, weights, tokens, state: PlainState | None = None, layers_out: l
         k_pos = torch.arange(state.k[run].shape[0])
         left = left_attend(q, state.k[run], state.v[run], p, k_pos, m["left"]) @ w[pre + ".mix.left.o"].T
         right = right_mixer(h, m["right"], w, pre + ".mix.right", eps, state.right[run])
-        mixed = float(m["left_scale"]) * left + float(m["right_scale"]) * right
+        mixed = keep(float(m["left_scale"]) * left + float(m["right_scale"]) * right)
         x = x + rms_norm(mixed, w[pre + ".norm1b"], eps)
         mlp = layer.get("mlp")
         if mlp:
-            h = rms_norm(x, w[pre + ".norm2"], eps)
-            y = glu(h, w, pre + ".mlp", True) if mlp["kind"] == "dense" else moe(h, w, pre + ".mlp", mlp)
+            h = keep(rms_norm(x, w[pre + ".norm2"], eps))
+            y = keep(glu(h, w, pre + ".mlp", True) if mlp["kind"] == "dense" else moe(h, w, pre + ".mlp", mlp, margins))
             x = x + rms_norm(y, w[pre + ".norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
