@@ -537,7 +537,31 @@ def rulunex_raw(sz: dict) -> dict:
             "layers": [{**k, "mlp": mlp} for k in kinds], "torch_dtype": "bfloat16"}
 
 
-DESIGNS = {"guvetar": guvetar_raw, "rulunex": rulunex_raw}
+def mifidra_raw(sz: dict) -> dict:
+    """Four layers, the middle two run twice: ``layers`` layer runs in all.  Every mixer is softmax attention beside
+    a gated delta rule; dense feed-forwards alternate with routed experts (16 experts of ff/8, 4 per token from 3 of
+    4 groups, beside a shared expert of ff/2: as many active feed-forward weights per token as the dense layers)."""
+    mixer = {
+        "left": {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": sz["head_dim"], "vdim": sz["head_dim"],
+                 "scale": sz["head_dim"] ** -0.5,
+                 "rot": {"base": 10000.0, "dims": sz["head_dim"],
+                         "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}},
+        "right": {"heads": sz["linear_heads"], "kv_heads": sz["linear_heads"], "dim": sz["linear_dim"],
+                  "vdim": sz["linear_vdim"], "conv": 4, "decay_rank": 64, "gate_rank": 64},
+        "left_scale": 0.7, "right_scale": 0.6}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": sz["ff"] // 8}, "shared": {"ff": sz["ff"] // 2},
+              "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 3}}}
+    times = 2
+    inner = (sz["layers"] - 2) // times
+    count = inner + 2
+    return {"architecture": "Mifidra", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-5},
+            "logit_scale": 1.0, "loop": {"start": 1, "stop": 1 + inner, "times": times},
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": routed if i % 2 else dense} for i in range(count)],
+            "torch_dtype": "bfloat16"}
+
+
+DESIGNS = {"guvetar": guvetar_raw, "rulunex": rulunex_raw, "mifidra": mifidra_raw}
 
 
 def llama_raw(sz: dict) -> dict:

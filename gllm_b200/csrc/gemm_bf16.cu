@@ -64,6 +64,16 @@ __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;
 
 struct Item {
   int a_row0, b_row0, split, tile_id;
+  int w_row0;      // first weight row of the tile in the weight's tensor map (b_row0, or that row of the tile's group)
+  bool skip;       // grouped: a tile of rows behind the last one in use
+};
+// Grouped products (normal orientation only): the rows of X come in tiles of BM that each belong to one group
+// (``group_of_tile[tile]``, ``num_tiles[0]`` tiles in use, both written on the device by the kernel before this one),
+// and group g multiplies by rows g * group_rows .. of W.  N is then the rows of ONE group.
+struct Groups {
+  const int* group_of_tile;
+  const int* num_tiles;
+  int group_rows;
 };
 // Work item w of a launch.  Normal: neighbouring CTAs share a weight tile.  Swapped:
 // neighbouring CTAs take the K ranges of the same weight rows.
@@ -76,6 +86,18 @@ __device__ __forceinline__ Item item_of(int w, int tiles_a, int splits) {
   it.a_row0 = ta * BM;
   it.b_row0 = tb * BN;
   it.tile_id = t;
+  it.w_row0 = SWAPPED ? it.a_row0 : it.b_row0;
+  it.skip = false;
+  return it;
+}
+template <int BN, bool SWAPPED>
+__device__ __forceinline__ Item item_of(int w, int tiles_a, int splits, const Groups& groups) {
+  Item it = item_of<BN, SWAPPED>(w, tiles_a, splits);
+  if (!SWAPPED && groups.group_of_tile != nullptr) {
+    const int ta = it.a_row0 / BM;
+    it.skip = ta >= groups.num_tiles[0];
+    if (!it.skip) it.w_row0 += groups.group_of_tile[ta] * groups.group_rows;
+  }
   return it;
 }
 
@@ -89,7 +111,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  OutT* __restrict__ out, int M, int N, int K, int64_t ldo, int splits, int kb_per_split,
                  int tiles_a, int num_items, float* __restrict__ partial, int* __restrict__ tickets,
-                 int reduce_in_kernel, int* __restrict__ status, int accumulate, GateAct act) {
+                 int reduce_in_kernel, int* __restrict__ status, int accumulate, GateAct act, Groups groups) {
   using S = Shape<BN>;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
@@ -136,6 +158,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t off_w = SWAPPED ? 0u : (uint32_t)S::STAGE_A, off_x = SWAPPED ? (uint32_t)S::STAGE_A : 0u;
       uint32_t it = 0;                                   // k-blocks issued so far, over all items
       bool ok = true;
+      if (groups.group_of_tile != nullptr) pdl_wait();   // which weight rows a tile needs comes from the kernel before
       // pass 0: the weight tiles of the first STAGES k-blocks; pass 1: their activation tiles, then
       // both operands of every later block as stages come free
       for (int pass = 0; pass < 2 && ok; ++pass) {
@@ -143,10 +166,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         it = 0;
         bool more = true;
         for (int w = blockIdx.x; w < num_items && ok && more; w += gridDim.x) {
-          const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
+          const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits, groups);
+          if (item.skip) continue;
           const int kb_begin = item.split * kb_per_split;
           const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
-          const int row_w = SWAPPED ? item.a_row0 : item.b_row0, row_x = SWAPPED ? item.b_row0 : item.a_row0;
+          const int row_w = item.w_row0, row_x = SWAPPED ? item.b_row0 : item.a_row0;
           for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
             const uint32_t s = it % S::STAGES, round = it / S::STAGES;
             const uint32_t bar = smem_addr(&full_bar[s]);
@@ -192,8 +216,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       constexpr uint32_t idesc = umma_idesc(BM, BN);
       uint32_t it = 0, n_used = 0;                       // k-blocks consumed; accumulators handed over
       bool ok = true;
+      if (groups.group_of_tile != nullptr) pdl_wait();
       for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
-        const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
+        const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits, groups);
+        if (item.skip) continue;
         const int kb_begin = item.split * kb_per_split;
         const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
         if (kb_end <= kb_begin) continue;                // an empty K range: the epilogue writes zeros
@@ -233,7 +259,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int ep_thread = (warp - 2) * 32 + lane;        // 0 .. 127
     uint32_t n_used = 0;
     for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
-      const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
+      const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits, groups);
+      if (item.skip) continue;
       const int kb_begin = item.split * kb_per_split;
       const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
       const bool has_k = kb_end > kb_begin;
@@ -464,11 +491,13 @@ int sm_count() { return gllm_sm_count(); }
 template <int BN, bool SWAPPED, typename OutT, bool GATED>
 int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
                 int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
-                cudaStream_t stream, int accumulate = 0, GateAct act = GateAct{1.f, 0.f, 0.f}) {
+                cudaStream_t stream, int accumulate = 0, GateAct act = GateAct{1.f, 0.f, 0.f},
+                Groups groups = Groups{nullptr, nullptr, 0}, int w_rows = 0) {
   using S = Shape<BN>;
   CUtensorMap map_a, map_b;
-  const bool ok = SWAPPED ? (make_map(&map_a, W, N, K, ldw, BM) && make_map(&map_b, X, M, K, ldx, BN))
-                          : (make_map(&map_a, X, M, K, ldx, BM) && make_map(&map_b, W, N, K, ldw, BN));
+  if (w_rows <= 0) w_rows = N;                 // grouped: the weight's map covers the rows of all groups
+  const bool ok = SWAPPED ? (make_map(&map_a, W, w_rows, K, ldw, BM) && make_map(&map_b, X, M, K, ldx, BN))
+                          : (make_map(&map_a, X, M, K, ldx, BM) && make_map(&map_b, W, w_rows, K, ldw, BN));
   if (!ok) return (int)cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
@@ -485,7 +514,7 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
   const int grid = num_items < sm_count() ? num_items : sm_count();
   return gllm_launch(umma_gemm_kernel<BN, SWAPPED, OutT, GATED>, dim3(grid), dim3(THREADS), (size_t)S::SMEM, stream, map_a,
                      map_b, out, M, N, K, ldo, splits, kb_per_split, tiles_a, num_items, partial, tickets,
-                     reduce_in_kernel, status, accumulate, act);
+                     reduce_in_kernel, status, accumulate, act, groups);
 }
 
 // Width of the weight tile for more than 64 tokens: 256 rows; 64 for a single tile of tokens (65 .. 128) times a
@@ -603,4 +632,31 @@ GLLM_API int gllm_gemm_bf16_accumulate(const __nv_bfloat16* X, const __nv_bfloat
   if (M <= 32) GLLM_ACC(32);
   GLLM_ACC(64);
 #undef GLLM_ACC
+}
+
+// Grouped product: the rows of X [rows, K] come in tiles of 128 that each belong to one group (``group_of_tile``,
+// ``num_tiles`` on the device); group g multiplies by W[g] of W [groups, N, K].  gated != 0: W[g]'s rows are blocks of
+// 64 gate rows and the 64 up rows of the same features and out is bf16 [rows, N / 2] = silu(gate) * up; otherwise out
+// is fp32 [rows, N].  Rows of tiles behind ``num_tiles[0]`` are neither read nor written; a row of X that no pair
+// owns gives a row of out that nobody reads (rows do not mix).
+GLLM_API int gllm_gemm_bf16_grouped(const __nv_bfloat16* X, const __nv_bfloat16* W, void* out, int gated, int rows, int N,
+                                    int K, int groups, const int* group_of_tile, const int* num_tiles, int wide,
+                                    int* status, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0 || groups <= 0) return 0;
+  if (rows % BM || K <= 0 || K % 8 || (gated && N % 128) || (reinterpret_cast<uintptr_t>(X) & 15) ||
+      (reinterpret_cast<uintptr_t>(W) & 15) || (int64_t)groups * N > 0x7fffffff)
+    return (int)cudaErrorInvalidValue;
+  const Groups g{group_of_tile, num_tiles, N};
+  const GateAct act{1.f, 0.f, 0.f};
+  const int w_rows = groups * N;
+#define GLLM_GROUPED(BN, OutT, GATED, ldo) \
+  return umma_launch<BN, false, OutT, GATED>(X, W, (OutT*)out, rows, N, K, K, K, ldo, 1, nullptr, nullptr, 0, status, \
+                                             stream, 0, act, g, w_rows)
+  if (gated) {
+    if (wide && N % 256 == 0) GLLM_GROUPED(256, __nv_bfloat16, true, N / 2);
+    GLLM_GROUPED(128, __nv_bfloat16, true, N / 2);
+  }
+  if (wide && N >= 256) GLLM_GROUPED(256, float, false, N);
+  GLLM_GROUPED(128, float, false, N);
+#undef GLLM_GROUPED
 }

@@ -113,7 +113,8 @@ moe_route_kernel(const float* __restrict__ logits, int64_t stride, const float* 
 
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ ids, int* __restrict__ sorted, int* __restrict__ tile_expert,
-                 int* __restrict__ num_tiles, int n_pairs, int experts, int tile_m, int max_tiles) {
+                 int* __restrict__ num_tiles, int* __restrict__ row_of_pair, int n_pairs, int experts, int tile_m,
+                 int max_tiles) {
   extern __shared__ int smi[];
   int* counts = smi;                  // [experts]
   int* first = counts + experts;      // [experts + 1] first row of every expert
@@ -146,7 +147,23 @@ moe_align_kernel(const int* __restrict__ ids, int* __restrict__ sorted, int* __r
     if (e < 0 || e >= experts) continue;
     const int row = first[e] + atomicAdd(&cursor[e], 1);
     if (row < max_tiles * tile_m) sorted[row] = p;
+    if (row_of_pair) row_of_pair[p] = min(row, max_tiles * tile_m - 1);
   }
+}
+
+// out[row_of_pair[p]] = x[p / top]: the tokens' rows in the order of the sorted pairs, for products that read
+// their rows in place (16 bytes a thread; width * sizeof(T) is a multiple of 16).
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const T* __restrict__ x, int64_t x_stride, const int* __restrict__ row_of_pair, T* __restrict__ out,
+                  int top, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const int p = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(p / top) * x_stride);
+  uint4* dst = reinterpret_cast<uint4*>(out + (int64_t)row_of_pair[p] * width);
+  const int n16 = width * (int)sizeof(T) / 16;
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
 }
 
 constexpr int MG_M = 16, MG_N = 64, MG_K = 32, MG_THREADS = 128;
@@ -226,13 +243,16 @@ moe_gemm_kernel(const T* __restrict__ a, int64_t a_stride, int a_div, const T* _
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const T* __restrict__ shared,
-                   T* __restrict__ out, int top, int width) {
+                   T* __restrict__ out, const int* __restrict__ row_of_pair, int top, int width) {
   pdl_trigger();
   pdl_wait();
   const int64_t t = blockIdx.x;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < top; ++s) acc = fmaf(weights[t * top + s], y[(t * top + s) * width + c], acc);
+    for (int s = 0; s < top; ++s) {
+      const int64_t row = row_of_pair ? (int64_t)row_of_pair[t * top + s] : t * top + s;
+      acc = fmaf(weights[t * top + s], y[row * width + c], acc);
+    }
     if (shared) acc += to_float(shared[t * width + c]);
     out[t * width + c] = from_float<T>(acc);
   }
@@ -265,14 +285,13 @@ GLLM_API int gllm_moe_route(const float* logits, int64_t stride, const float* co
                      experts, top, groups, keep, renorm);
 }
 
-GLLM_API int gllm_moe_align(const int* ids, int* sorted, int* tile_expert, int* num_tiles, int* reserved, int n_pairs,
-                            int experts, int tile_m, int max_tiles, cudaStream_t stream) {
-  (void)reserved;
+GLLM_API int gllm_moe_align(const int* ids, int* sorted, int* tile_expert, int* num_tiles, int* row_of_pair,
+                            int n_pairs, int experts, int tile_m, int max_tiles, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
   const size_t smem = sizeof(int) * (size_t)(3 * experts + 1);
   if (smem > 48 * 1024 || tile_m < 1 || max_tiles < 1) return (int)cudaErrorInvalidValue;
-  return gllm_launch(moe_align_kernel, dim3(1), dim3(1024), smem, stream, ids, sorted, tile_expert, num_tiles, n_pairs,
-                     experts, tile_m, max_tiles);
+  return gllm_launch(moe_align_kernel, dim3(1), dim3(1024), smem, stream, ids, sorted, tile_expert, num_tiles, row_of_pair,
+                     n_pairs, experts, tile_m, max_tiles);
 }
 
 GLLM_API int gllm_moe_gemm_f32(const float* a, int64_t a_stride, int a_div, const float* w, int64_t w_expert_stride,
@@ -289,15 +308,23 @@ GLLM_API int gllm_moe_gemm_bf16(const __nv_bfloat16* a, int64_t a_stride, int a_
                                         num_tiles, out, max_tiles, n_cols, k, tile_m, stream);
 }
 
-GLLM_API int gllm_moe_combine_f32(const float* y, const float* weights, const float* shared, float* out, int n_tokens,
-                                  int top, int width, cudaStream_t stream) {
+GLLM_API int gllm_moe_combine_f32(const float* y, const float* weights, const float* shared, float* out,
+                                  const int* row_of_pair, int n_tokens, int top, int width, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  return gllm_launch(moe_combine_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, y, weights, shared, out, top,
-                     width);
+  return gllm_launch(moe_combine_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, y, weights, shared, out,
+                     row_of_pair, top, width);
 }
 GLLM_API int gllm_moe_combine_bf16(const float* y, const float* weights, const __nv_bfloat16* shared,
-                                   __nv_bfloat16* out, int n_tokens, int top, int width, cudaStream_t stream) {
+                                   __nv_bfloat16* out, const int* row_of_pair, int n_tokens, int top, int width,
+                                   cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   return gllm_launch(moe_combine_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, y, weights, shared, out,
+                     row_of_pair, top, width);
+}
+GLLM_API int gllm_moe_gather_bf16(const __nv_bfloat16* x, int64_t x_stride, const int* row_of_pair, __nv_bfloat16* out,
+                                  int n_pairs, int top, int width, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (width % 8 || x_stride % 8 || top < 1 || (reinterpret_cast<uintptr_t>(x) & 15)) return (int)cudaErrorInvalidValue;
+  return gllm_launch(moe_gather_kernel<__nv_bfloat16>, dim3(n_pairs), dim3(256), 0, stream, x, x_stride, row_of_pair, out,
                      top, width);
 }

@@ -398,6 +398,64 @@ def stream_mix_norm(rows=2048, hidden=2048, streams=4, iters=5, peaks=None):
                    rows * hidden * (8 * streams + 4))
 
 
+def delta_rule(tokens=2048, batch=1, heads=16, dk=64, dv=128, taps=4, prep=0, iters=5, peaks=None):
+    """The gated delta rule's recurrence over ``batch`` requests of ``tokens`` tokens (tokens=1: a decode step);
+    ``prep=1`` times the kernel before it instead (convolution, SiLU, unit norms, decays, beta)."""
+    from gllm_b200.ops import stateful
+
+    n = batch * tokens
+    channels = 2 * heads * dk + heads * dv
+    b = _Batch(batch, tokens, 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    shape = dict(tokens=tokens, batch=batch, heads=heads, dk=dk, dv=dv)
+    x = torch.randn(n, channels, device="cuda").to(torch.bfloat16)
+    conv_w = torch.randn(channels, taps, device="cuda") * 0.5
+    conv_state = torch.zeros(batch + 1, taps - 1, channels, device="cuda")
+    raw, braw = torch.randn(n, heads * dk, device="cuda"), torch.randn(n, heads, device="cuda")
+    dt_bias, A_log = torch.zeros(heads * dk, device="cuda"), torch.full((heads,), -3.0, device="cuda")
+    run_prep = lambda: stateful.delta_prep(x, conv_w, conv_state, b.positions, b.token_row, b.cu_q, b.state_slots, batch,
+                                           raw, dt_bias, A_log, braw, heads, heads, dk, dv, 1e-6, dk ** -0.5)
+    if prep:
+        us = _time(run_prep, iters, flush)
+        nbytes = n * (channels * 2 + heads * dk * 4 + heads * 4) + n * (channels + heads * dk + heads) * 4
+        return _result("delta_prep", us, peaks, dict(shape, taps=taps), nbytes)
+    qk, v, g, beta = run_prep()
+    state = torch.zeros(batch + 1, heads, dv, dk, device="cuda")
+    fn = lambda: stateful.delta_rule(qk, v, g, beta, state, b.cu_q, b.state_slots, batch, heads, heads, dk, dv,
+                                     max_q_len=tokens)
+    us = _time(fn, iters, flush)
+    nbytes = 2 * batch * heads * dk * dv * 4 + n * heads * (3 * dk + 2 * dv + 1) * 4
+    return _result("delta_rule", us, peaks, shape, nbytes, 6.0 * n * heads * dk * dv)
+
+
+def routed_experts(tokens=2048, width=2048, ff=1024, experts=16, top=4, groups=4, keep=3, mma=1, iters=5, peaks=None):
+    """Routing, sorting the pairs by expert, both expert products and the weighted sum of ``tokens`` tokens
+    (``mma=0``: the CUDA-core products)."""
+    from gllm_b200 import ops
+    from gllm_b200.ops import moe
+
+    x = (torch.randn(tokens, width, device="cuda") * 0.5).to(torch.bfloat16)
+    w_gu = (torch.randn(experts, 2 * ff, width, device="cuda") * width ** -0.5).to(torch.bfloat16)
+    w_d = (torch.randn(experts, width, ff, device="cuda") * ff ** -0.5).to(torch.bfloat16)
+    logits = torch.randn(tokens, experts, device="cuda")
+    correction = torch.zeros(experts, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    tensor_cores = bool(mma) and moe.tensor_cores_take(torch.bfloat16, width, ff)
+    if tensor_cores:
+        w_gu = torch.stack([ops.interleave_gate_up(w[:ff], w[ff:]) for w in w_gu]).contiguous()
+
+    def fn():
+        ids, weights = moe.route(logits, correction, top, groups, keep)
+        return moe.apply_experts(x, ids, weights, w_gu, w_d, None, tensor_cores)
+
+    us = _time(fn, iters, flush)
+    used = min(experts, tokens * top)
+    nbytes = used * 3 * ff * width * 2 + tokens * width * 4 + tokens * top * (ff * 4 + width * 8)
+    return _result("routed_experts", us, peaks, dict(tokens=tokens, width=width, ff=ff, experts=experts, top=top), nbytes,
+                   6.0 * tokens * top * ff * width)
+
+
 KERNELS = {
     "attention_decode": attention_decode,
     "attention_prefill": attention_prefill,
@@ -413,6 +471,8 @@ KERNELS = {
     "selective_scan": selective_scan,
     "conv_silu": conv_silu,
     "stream_mix_norm": stream_mix_norm,
+    "delta_rule": delta_rule,
+    "routed_experts": routed_experts,
 }
 
 

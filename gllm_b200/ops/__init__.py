@@ -120,7 +120,8 @@ _SIGNATURES = {
         "gllm_moe_route": [P, c_int64, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
         "gllm_moe_align": [P, P, P, P, P, c_int, c_int, c_int, c_int, P],
         "gllm_moe_gemm_{t}": [P, c_int64, c_int, P, c_int64, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, P],
-        "gllm_moe_combine_{t}": [P, P, P, P, c_int, c_int, c_int, P],
+        "gllm_moe_combine_{t}": [P, P, P, P, P, c_int, c_int, c_int, P],
+        "gllm_moe_gather_{t}": [P, c_int64, P, P, c_int, c_int, c_int, P],
     },
     "attention_simt": {
         "gllm_attention_simt_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,

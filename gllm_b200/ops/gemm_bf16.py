@@ -57,6 +57,34 @@ def _accumulate_fn():
     return _accumulate
 
 
+_grouped = None
+
+
+def linear_grouped(x: torch.Tensor, weight: torch.Tensor, group_of_tile: torch.Tensor, num_tiles: torch.Tensor,
+                   gated: bool, wide: bool) -> torch.Tensor:
+    """``out[r] = x[r] @ weight[g(r)].T`` on the tcgen05 kernel, the rows of ``x [rows, k]`` (bf16, ``rows`` a
+    multiple of 128) coming in tiles of 128 that each belong to one group: ``group_of_tile [rows / 128]`` and
+    ``num_tiles [1]`` (int32, on the device; tiles behind ``num_tiles`` are neither read nor written).  ``weight
+    [groups, n, k]``; ``gated``: every group's rows are stacked by ``interleave_gate_up`` and the result is bf16
+    ``silu(gate) * up`` ``[rows, n / 2]``; otherwise fp32 ``[rows, n]``.  ``wide``: tiles of 256 weight rows (many
+    rows per group) instead of 128."""
+    global _grouped
+    if _grouped is None:
+        f = load_module("gemm_bf16").gllm_gemm_bf16_grouped
+        f.argtypes = [P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, c_int, P, P]
+        f.restype = c_int
+        _grouped = f
+    from gllm_b200.ops import _check, _stream, status_word
+
+    rows, k = x.shape
+    groups, n, _ = weight.shape
+    out = torch.empty((rows, n // 2 if gated else n), dtype=torch.bfloat16 if gated else torch.float32, device=x.device)
+    _check(_grouped(x.data_ptr(), weight.data_ptr(), out.data_ptr(), int(gated), rows, n, k, groups,
+                    group_of_tile.data_ptr(), num_tiles.data_ptr(), int(wide), status_word(x.device).data_ptr(),
+                    _stream()), "linear_grouped")
+    return out
+
+
 def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
     """Per-device scratch of the split-K reduction: fp32 partial tiles (two
     buffers used in turn, so an unsummed result survives the next product) and

@@ -9,6 +9,7 @@ import torch
 from gllm_b200.ops import _check, _cuda, _fn, _ptr, _stream, _suffix
 
 TILE_ROWS = 16        # rows of one tile of the expert products: an expert's pairs are padded to a multiple of it
+TENSOR_CORE_TILE_ROWS = 128     # the same for the tcgen05 products (the rows of one accumulator tile)
 
 
 def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int = 1, groups_kept: int = 1,
@@ -33,19 +34,40 @@ def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, group
     return ids, weights
 
 
-def align(ids: torch.Tensor, experts: int):
-    """The (token, slot) pairs sorted by expert in tiles of ``TILE_ROWS`` rows: ``(sorted [max_tiles * TILE_ROWS]``
-    (pair index or -1), ``tile_expert [max_tiles]``, ``num_tiles [1])``, all int32 on the device."""
+def align(ids: torch.Tensor, experts: int, tile_rows: int = TILE_ROWS, want_rows: bool = False):
+    """The (token, slot) pairs sorted by expert in tiles of ``tile_rows`` rows: ``(sorted [max_tiles * tile_rows]``
+    (pair index or -1), ``tile_expert [max_tiles]``, ``num_tiles [1])``, all int32 on the device; with
+    ``want_rows`` also ``row_of_pair [pairs]``, the row each pair got."""
     _cuda(ids, "ids", torch.int32)
     pairs = ids.numel()
-    max_tiles = -(-pairs // TILE_ROWS) + min(experts, pairs)
-    sorted_pairs = torch.empty(max_tiles * TILE_ROWS, dtype=torch.int32, device=ids.device)
+    max_tiles = -(-pairs // tile_rows) + min(experts, pairs)
+    sorted_pairs = torch.empty(max_tiles * tile_rows, dtype=torch.int32, device=ids.device)
     tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=ids.device)
     num_tiles = torch.empty(1, dtype=torch.int32, device=ids.device)
+    row_of_pair = torch.empty(pairs, dtype=torch.int32, device=ids.device) if want_rows else None
     _check(_fn("moe", "gllm_moe_align")(ids.data_ptr(), sorted_pairs.data_ptr(), tile_expert.data_ptr(),
-                                        num_tiles.data_ptr(), None, pairs, int(experts), TILE_ROWS, max_tiles,
-                                        _stream()), "moe_align")
+                                        num_tiles.data_ptr(), _ptr(row_of_pair), pairs, int(experts), int(tile_rows),
+                                        max_tiles, _stream()), "moe_align")
+    if want_rows:
+        return sorted_pairs, tile_expert, num_tiles, row_of_pair
     return sorted_pairs, tile_expert, num_tiles
+
+
+def gather_rows(x: torch.Tensor, top: int, row_of_pair: torch.Tensor, rows: int) -> torch.Tensor:
+    """``out[row_of_pair[p]] = x[p // top]`` (bf16, ``[rows, width]``): the tokens' rows in the order of the sorted
+    pairs.  Rows that no pair owns are left as they are: the products' rows do not mix, and nobody reads theirs."""
+    _cuda(x, "x", torch.bfloat16, contiguous=False)
+    _cuda(row_of_pair, "row_of_pair", torch.int32)
+    out = torch.empty((rows, x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(_fn("moe", "gllm_moe_gather_bf16")(x.data_ptr(), x.stride(0), row_of_pair.data_ptr(), out.data_ptr(),
+                                              row_of_pair.numel(), int(top), x.shape[1], _stream()), "moe_gather")
+    return out
+
+
+def tensor_cores_take(dtype: torch.dtype, width: int, ff: int) -> bool:
+    """Whether the experts' products run on the tcgen05 kernel: bf16, rows that start on 16 bytes, and gate and up
+    rows stacked in blocks of 64."""
+    return dtype == torch.bfloat16 and width % 8 == 0 and ff % 64 == 0
 
 
 def expert_product(a: torch.Tensor, rows_per_input: int, weight: torch.Tensor, plan, n_pairs: int, gated: bool):
@@ -69,13 +91,17 @@ def expert_product(a: torch.Tensor, rows_per_input: int, weight: torch.Tensor, p
     return out
 
 
-def combine(y: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
-    """``out[t] = sum_s weights[t, s] * y[t * top + s] (+ shared[t])``, summed in slot order in fp32."""
+def combine(y: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None, out_dtype: torch.dtype,
+            row_of_pair: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = sum_s weights[t, s] * y[t * top + s] (+ shared[t])``, summed in slot order in fp32; with
+    ``row_of_pair`` the pair's result is row ``row_of_pair[t * top + s]`` of ``y``."""
     _cuda(y, "y", torch.float32)
     _cuda(weights, "weights", torch.float32)
     n, top = weights.shape
     width = y.shape[1]
-    if y.shape[0] != n * top:
+    if row_of_pair is not None:
+        _cuda(row_of_pair, "row_of_pair", torch.int32)
+    if (y.shape[0] != n * top and row_of_pair is None) or (row_of_pair is not None and row_of_pair.numel() != n * top):
         raise ValueError("one result row per (token, slot) pair is needed")
     if shared is not None:
         _cuda(shared, "shared", out_dtype)
@@ -83,5 +109,29 @@ def combine(y: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None,
             raise ValueError("the shared expert's result does not fit")
     out = torch.empty((n, width), dtype=out_dtype, device=y.device)
     _check(_fn("moe", f"gllm_moe_combine_{_suffix(out_dtype)}")(y.data_ptr(), weights.data_ptr(), _ptr(shared),
-                                                               out.data_ptr(), n, top, width, _stream()), "moe_combine")
+                                                               out.data_ptr(), _ptr(row_of_pair), n, top, width,
+                                                               _stream()), "moe_combine")
     return out
+
+
+def apply_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                  w_down: torch.Tensor, shared: torch.Tensor | None, tensor_cores: bool) -> torch.Tensor:
+    """``out[t] = sum_s weights[t, s] * expert_{ids[t, s]}(x[t]) (+ shared[t])`` with ``expert_e(x) = w_down[e]
+    (silu(gate) * up)``.  ``tensor_cores``: ``w_gate_up [experts, 2 * ff, width]`` is stacked per expert by
+    ``interleave_gate_up``; the tokens' rows are copied into the order of the sorted pairs, both products read and
+    write rows in that order on the tcgen05 kernel, and the weighted sum looks every pair's row up.  Otherwise
+    ``w_gate_up`` holds an expert's gate rows, then its up rows, and the CUDA-core kernel runs."""
+    experts, (_, top), pairs = w_gate_up.shape[0], ids.shape, ids.numel()
+    if not tensor_cores:
+        plan = align(ids, experts)
+        hidden = expert_product(x, top, w_gate_up, plan, pairs, gated=True)
+        y = expert_product(hidden, 1, w_down, plan, pairs, gated=False)
+        return combine(y, weights, shared, x.dtype)
+    from gllm_b200.ops import gemm_bf16
+
+    _, tile_expert, num_tiles, row_of_pair = align(ids, experts, TENSOR_CORE_TILE_ROWS, want_rows=True)
+    wide = pairs > 2048
+    xs = gather_rows(x, top, row_of_pair, tile_expert.numel() * TENSOR_CORE_TILE_ROWS)
+    hidden = gemm_bf16.linear_grouped(xs, w_gate_up, tile_expert, num_tiles, gated=True, wide=wide)
+    y = gemm_bf16.linear_grouped(hidden, w_down, tile_expert, num_tiles, gated=False, wide=wide)
+    return combine(y, weights, shared, x.dtype, row_of_pair)

@@ -6,7 +6,9 @@ Router logits ``z = W_router x`` in fp32; scores ``s = sigmoid(z)``.  The choice
 best of ``groups`` equal groups of neighbouring experts, a group's score being the sum of its two largest choice
 scores.  The result is ``sum_e s_e * expert_e(x)`` over the chosen experts (weights divided by their sum with
 ``renormalize``) plus the shared expert's.  The (token, expert) pairs are sorted by expert on the device and the
-experts' products run over tiles of one expert each (``csrc/moe.cu``); nothing about the choice reaches the host.
+experts' products run over tiles of one expert each: in bf16, with sizes it takes, on the tcgen05 kernel of the dense
+products in its grouped form (tiles of 128 rows, ``csrc/gemm_bf16.cu``), otherwise on a CUDA-core kernel (tiles of
+16 rows, ``csrc/moe.cu``); nothing about the choice reaches the host.
 """
 
 from __future__ import annotations
@@ -40,9 +42,10 @@ class RoutedExperts(FeedForward):
         self.renormalize, self.has_correction = bool(renormalize), bool(correction)
         self.shared = build_part(FEED_FORWARDS, shared) if shared is not None else None
         self.w_router = self.correction = self.w_gate_up = self.w_down = None
+        self.tensor_cores = False
 
     def kernel_needs(self):
-        needs = {"modules": {"moe"}}
+        needs = {"modules": {"moe"}}      # (the tensor-core products are the dense ones' module, which bf16 loads)
         if self.shared is not None:
             for key, values in self.shared.kernel_needs().items():
                 needs.setdefault(key, set()).update(values)
@@ -68,9 +71,11 @@ class RoutedExperts(FeedForward):
         self.w_router = get(self.names["router"], "matrix").contiguous()
         if self.has_correction:
             self.correction = get(self.names["correction"], "bias").contiguous()
-        # [experts, 2 * ff, width]: an expert's gate rows, then its up rows; [experts, width, ff]
-        self.w_gate_up = torch.stack([torch.cat([get(self._expert(e, "gate"), "matrix"),
-                                                 get(self._expert(e, "up"), "matrix")], 0)
+        # [experts, 2 * ff, width]: an expert's gate rows, then its up rows (for the tensor-core products: blocks of
+        # 64 gate rows and the 64 up rows of the same features); [experts, width, ff]
+        self.tensor_cores = moe.tensor_cores_take(dtype, self.hidden_size, self.intermediate_size)
+        stack = ops.interleave_gate_up if self.tensor_cores else (lambda gate, up: torch.cat([gate, up], 0))
+        self.w_gate_up = torch.stack([stack(get(self._expert(e, "gate"), "matrix"), get(self._expert(e, "up"), "matrix"))
                                       for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([get(self._expert(e, "down"), "matrix") for e in range(self.experts)]).contiguous()
         if self.shared is not None:
@@ -79,13 +84,9 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
         ids, weights = moe.route(logits, self.correction, self.top, self.groups, self.groups_kept, self.renormalize)
-        plan = moe.align(ids, self.experts)
-        pairs = ids.numel()
-        hidden = moe.expert_product(x, self.top, self.w_gate_up, plan, pairs, gated=True)
-        y = moe.expert_product(hidden, 1, self.w_down, plan, pairs, gated=False)
         shared = None
         if self.shared is not None:
             sink, ctx.residual_sink = getattr(ctx, "residual_sink", None), None
             shared = ops.as_tensor(self.shared.forward(x, ctx))
             ctx.residual_sink = sink
-        return moe.combine(y, weights, shared, x.dtype)
+        return moe.apply_experts(x, ids, weights, self.w_gate_up, self.w_down, shared, self.tensor_cores)

@@ -198,6 +198,32 @@ def test_expert_products(dtype, n, width, ff, experts, top):
     assert float((out - want).abs().max()) <= tol * max(1.0, float(want.abs().max()))
 
 
+@pytest.mark.parametrize("n,width,ff,experts,top", [(37, 64, 64, 8, 2), (1, 48, 64, 4, 1), (700, 128, 192, 16, 4),
+                                                     (3000, 256, 128, 4, 2), (5, 40, 128, 6, 6)])
+def test_expert_products_on_the_tensor_cores(n, width, ff, experts, top):
+    """The same through the grouped tcgen05 products: rows copied into the order of the sorted pairs (tiles of 128
+    rows of one expert, the last one of an expert partly empty), results looked up per pair; some experts unused."""
+    from gllm_b200 import ops
+    from gllm_b200.ops import moe
+
+    assert moe.tensor_cores_take(torch.bfloat16, width, ff)
+    g = torch.Generator().manual_seed(n)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).float()
+    x, wg, wu = rnd(n, width), rnd(experts, ff, width) / math.sqrt(width), rnd(experts, ff, width) / math.sqrt(width)
+    wd, shared = rnd(experts, width, ff) / math.sqrt(ff), rnd(n, width)
+    usable = max(top, experts - 1)                                # the last expert stays unused where there is room
+    ids = torch.stack([torch.randperm(usable, generator=g)[:top] for _ in range(n)]).to(torch.int32)
+    wts = torch.rand(n, top, generator=g)
+    gate, up = torch.einsum("tw,efw->tef", x.to(F), wg.to(F)), torch.einsum("tw,efw->tef", x.to(F), wu.to(F))
+    hidden = (torch.nn.functional.silu(gate) * up).to(torch.bfloat16).to(F)
+    each = torch.einsum("tef,ewf->tew", hidden, wd.to(F))
+    want = shared.to(F) + (each.gather(1, ids.long()[:, :, None].expand(n, top, width)) * wts.to(F)[:, :, None]).sum(1)
+    stacked = torch.stack([ops.interleave_gate_up(wg[e], wu[e]) for e in range(experts)]).to(torch.bfloat16).cuda()
+    out = moe.apply_experts(x.to(torch.bfloat16).cuda(), ids.cuda(), wts.cuda(), stacked, wd.to(torch.bfloat16).cuda(),
+                            shared.to(torch.bfloat16).cuda(), True).double().cpu()
+    assert float((out - want).abs().max()) <= 2e-2 * max(1.0, float(want.abs().max()))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,stored,dims,scaled", [(4, 2, 32, 32, 32, True), (2, 1, 24, 32, 16, False),
                                                                    (3, 3, 12, 32, 0, False), (1, 1, 36, 64, 36, True),
