@@ -96,84 +96,142 @@ conv_state_update_kernel(const T* __restrict__ x, int64_t x_stride, float* __res
 }
 
 constexpr int DELTA_THREADS = 128;
-constexpr int DELTA_CHUNK = 16;
+constexpr int DELTA_MAX_CHUNK = 16;
 
-template <int DPT>
+// Asynchronous copies global -> shared: a chunk's operands are on their way while the chunk before it is computed.
+__device__ __forceinline__ void copy_async(float* dst, const float* src, int floats) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  if (floats == 4) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Tokens are taken in chunks of `tc`, in two buffers: q [tc][dkp], k [tc][dkp], g [tc][dkp], v [tc][cols], beta [tc]
+// (dkp = lanes * DPT >= dk; what lies beyond dk or dv is zeroed once and never copied over).  VEC = 4 copies and
+// reads four floats at a time, which needs dk and dv to be multiples of 4 (all row starts are then 16-byte aligned).
+// Per token the chain from state to state is: dot products with the decayed key and query (the decay is folded
+// into them, off the chain), their sums over the column's lanes, u, one fused multiply-add per state element.
+template <int DPT, int VEC>
 __global__ void __launch_bounds__(DELTA_THREADS)
 delta_rule_kernel(const float* __restrict__ qk, const float* __restrict__ v, const float* __restrict__ g,
                   const float* __restrict__ beta, float* __restrict__ state, const int* __restrict__ cu_q,
                   const int* __restrict__ state_slots, float* __restrict__ out, int heads, int kv_heads, int dk,
-                  int dv, int lanes) {
-  extern __shared__ float sm[];
+                  int dv, int lanes, int tc) {
+  extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   pdl_wait();
   const int cols = DELTA_THREADS / lanes, dkp = lanes * DPT;
   const int r = blockIdx.z, h = blockIdx.y, hg = h / (heads / kv_heads);
-  const int col = blockIdx.x * cols + threadIdx.x / lanes, sub = threadIdx.x % lanes;
+  const int cix = threadIdx.x / lanes, sub = threadIdx.x % lanes;
+  const int col0 = blockIdx.x * cols, col = col0 + cix;
   const bool live = col < dv;
   const int t0 = cu_q[r], t1 = cu_q[r + 1];
   if (t1 <= t0) return;
-  float* qs = sm;                                   // [chunk][dkp]
-  float* ks = qs + DELTA_CHUNK * dkp;
-  float* gs = ks + DELTA_CHUNK * dkp;
-  float* vs = gs + DELTA_CHUNK * dkp;               // [chunk][cols]
-  float* bs = vs + DELTA_CHUNK * cols;              // [chunk]
+  const int buf_floats = (tc * (3 * dkp + cols + 1) + 3) & ~3;
+  for (int i = threadIdx.x; i < 2 * buf_floats; i += DELTA_THREADS) sm[i] = 0.f;
   float S[DPT];
-  float* sp = state + (((int64_t)state_slots[r] * heads + h) * dv + (live ? col : 0)) * dk;
+  float* sp = state + (((int64_t)state_slots[r] * heads + h) * dv + (live ? col : 0)) * dk + sub * DPT;
+  if (VEC == 4) {
 #pragma unroll
-  for (int e = 0; e < DPT; ++e) {
-    const int d = sub * DPT + e;
-    S[e] = live && d < dk ? sp[d] : 0.f;
+    for (int e = 0; e < DPT; e += 4) {
+      const float4 x = live && sub * DPT + e < dk ? *reinterpret_cast<const float4*>(sp + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[e] = x.x, S[e + 1] = x.y, S[e + 2] = x.z, S[e + 3] = x.w;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < DPT; ++e) S[e] = live && sub * DPT + e < dk ? sp[e] : 0.f;
   }
   const int qk_cols = 2 * kv_heads * dk;
-  for (int c0 = t0; c0 < t1; c0 += DELTA_CHUNK) {
-    const int tc = min(DELTA_CHUNK, t1 - c0);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < tc * dkp; idx += DELTA_THREADS) {
-      const int t = idx / dkp, d = idx - t * dkp;
-      const bool ok = d < dk;
+  const int dkv = dk / VEC, colv = cols / VEC;            // cols is a power of two >= 4
+  const float* q_src = qk + hg * dk;
+  const float* k_src = qk + (kv_heads + hg) * dk;
+  const float* g_src = g + (int64_t)h * dk;
+  const float* v_src = v + (int64_t)h * dv + col0;
+  auto issue = [&](int c0, int nt, float* buf) {
+    float* qs = buf;
+    float* ks = qs + tc * dkp;
+    float* gs = ks + tc * dkp;
+    float* vs = gs + tc * dkp;
+    float* bs = vs + tc * cols;
+    for (int idx = threadIdx.x; idx < nt * dkv; idx += DELTA_THREADS) {
+      const int t = idx / dkv, d = (idx - t * dkv) * VEC;
       const int64_t tok = c0 + t;
-      qs[idx] = ok ? qk[tok * qk_cols + hg * dk + d] : 0.f;
-      ks[idx] = ok ? qk[tok * qk_cols + (kv_heads + hg) * dk + d] : 0.f;
-      gs[idx] = ok ? g[(tok * heads + h) * dk + d] : 0.f;
+      copy_async(qs + t * dkp + d, q_src + tok * qk_cols + d, VEC);
+      copy_async(ks + t * dkp + d, k_src + tok * qk_cols + d, VEC);
+      copy_async(gs + t * dkp + d, g_src + tok * heads * dk + d, VEC);
     }
-    for (int idx = threadIdx.x; idx < tc * cols; idx += DELTA_THREADS) {
-      const int t = idx / cols, c = blockIdx.x * cols + (idx - t * cols);
-      vs[idx] = c < dv ? v[((int64_t)(c0 + t) * heads + h) * dv + c] : 0.f;
+    for (int idx = threadIdx.x; idx < nt * colv; idx += DELTA_THREADS) {
+      const int t = idx / colv, c = (idx - t * colv) * VEC;
+      if (col0 + c < dv) copy_async(vs + t * cols + c, v_src + (int64_t)(c0 + t) * heads * dv + c, VEC);
     }
-    for (int t = threadIdx.x; t < tc; t += DELTA_THREADS) bs[t] = beta[(int64_t)(c0 + t) * heads + h];
+    for (int t = threadIdx.x; t < nt; t += DELTA_THREADS) copy_async(bs + t, beta + (int64_t)(c0 + t) * heads + h, 1);
+    copy_async_commit();
+  };
+  __syncthreads();                                         // the zeros are there before the first copy lands
+  issue(t0, min(tc, t1 - t0), sm);
+  int which = 0;
+  for (int c0 = t0; c0 < t1; c0 += tc, which ^= 1) {
+    const int nt = min(tc, t1 - c0);
+    if (c0 + tc < t1) {
+      issue(c0 + tc, min(tc, t1 - c0 - tc), sm + (which ^ 1) * buf_floats);
+      copy_async_wait<1>();
+    } else {
+      copy_async_wait<0>();
+    }
     __syncthreads();
-    for (int t = 0; t < tc; ++t) {
-      const float* qt = qs + t * dkp + sub * DPT;
-      const float* kt = ks + t * dkp + sub * DPT;
-      const float* gt = gs + t * dkp + sub * DPT;
-      float kk[DPT], qq[DPT];
+    const float* buf = sm + which * buf_floats;
+    const float* qs = buf + sub * DPT;
+    const float* ks = qs + tc * dkp;
+    const float* gs = ks + tc * dkp;
+    const float* vs = buf + 3 * tc * dkp + cix;
+    const float* bs = buf + 3 * tc * dkp + tc * cols;
+    float* op = out + ((int64_t)c0 * heads + h) * dv + col;
+    for (int t = 0; t < nt; ++t) {
+      float kk[DPT], gg[DPT];
       float sk = 0.f, sq = 0.f, kq = 0.f;
+      if (VEC == 4) {
+#pragma unroll
+        for (int e = 0; e < DPT; e += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(ks + t * dkp + e);
+          const float4 b = *reinterpret_cast<const float4*>(gs + t * dkp + e);
+          kk[e] = a.x, kk[e + 1] = a.y, kk[e + 2] = a.z, kk[e + 3] = a.w;
+          gg[e] = b.x, gg[e + 1] = b.y, gg[e + 2] = b.z, gg[e + 3] = b.w;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < DPT; ++e) kk[e] = ks[t * dkp + e], gg[e] = gs[t * dkp + e];
+      }
 #pragma unroll
       for (int e = 0; e < DPT; ++e) {
-        kk[e] = kt[e];
-        qq[e] = qt[e];
-        S[e] *= gt[e];
-        sk = fmaf(S[e], kk[e], sk);
-        sq = fmaf(S[e], qq[e], sq);
-        kq = fmaf(kk[e], qq[e], kq);
+        const float qe = qs[t * dkp + e];
+        sk = fmaf(S[e], gg[e] * kk[e], sk);
+        sq = fmaf(S[e], gg[e] * qe, sq);
+        kq = fmaf(kk[e], qe, kq);
       }
       for (int o = lanes >> 1; o > 0; o >>= 1) {
         sk += __shfl_xor_sync(0xffffffffu, sk, o);
         sq += __shfl_xor_sync(0xffffffffu, sq, o);
         kq += __shfl_xor_sync(0xffffffffu, kq, o);
       }
-      const float u = bs[t] * (vs[t * cols + threadIdx.x / lanes] - sk);
+      const float u = bs[t] * (vs[t * cols] - sk);
 #pragma unroll
-      for (int e = 0; e < DPT; ++e) S[e] = fmaf(kk[e], u, S[e]);
-      if (sub == 0 && live) out[((int64_t)(c0 + t) * heads + h) * dv + col] = fmaf(u, kq, sq);
+      for (int e = 0; e < DPT; ++e) S[e] = fmaf(kk[e], u, gg[e] * S[e]);
+      if (sub == 0 && live) op[(int64_t)t * heads * dv] = fmaf(u, kq, sq);
     }
+    __syncthreads();                                       // the next copies go into the buffer just read
   }
   if (live) {
+    if (VEC == 4) {
 #pragma unroll
-    for (int e = 0; e < DPT; ++e) {
-      const int d = sub * DPT + e;
-      if (d < dk) sp[d] = S[e];
+      for (int e = 0; e < DPT; e += 4)
+        if (sub * DPT + e < dk) *reinterpret_cast<float4*>(sp + e) = make_float4(S[e], S[e + 1], S[e + 2], S[e + 3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < DPT; ++e)
+        if (sub * DPT + e < dk) sp[e] = S[e];
     }
   }
 }
@@ -216,15 +274,23 @@ int delta_rule_launch(const float* qk, const float* v, const float* g, const flo
   const int dpt = dk <= 128 ? 4 : (dk <= 256 ? 8 : 16);
   const int lanes = pow2_at_least((dk + dpt - 1) / dpt);
   const int cols = DELTA_THREADS / lanes, dkp = lanes * dpt;
-  const size_t smem = sizeof(float) * (size_t)DELTA_CHUNK * (3 * dkp + cols + 1);
-  void (*kernel)(const float*, const float*, const float*, const float*, float*, const int*, const int*, float*, int, int,
-                 int, int, int) = dpt == 4 ? delta_rule_kernel<4> : (dpt == 8 ? delta_rule_kernel<8> : delta_rule_kernel<16>);
+  int tc = DELTA_MAX_CHUNK;
+  while (tc > 2 && 2 * tc * (3 * dkp + cols + 1) * sizeof(float) > 96 * 1024) tc >>= 1;
+  const size_t smem = sizeof(float) * 2 * (size_t)((tc * (3 * dkp + cols + 1) + 3) & ~3);
+  const bool vec = dk % 4 == 0 && dv % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(qk) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(g) |
+                     reinterpret_cast<uintptr_t>(state)) & 15) == 0;
+  using Kernel = void (*)(const float*, const float*, const float*, const float*, float*, const int*, const int*, float*,
+                          int, int, int, int, int, int);
+  Kernel kernel = dpt == 4 ? (vec ? delta_rule_kernel<4, 4> : delta_rule_kernel<4, 1>)
+                           : (dpt == 8 ? (vec ? delta_rule_kernel<8, 4> : delta_rule_kernel<8, 1>)
+                                       : (vec ? delta_rule_kernel<16, 4> : delta_rule_kernel<16, 1>));
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   return gllm_launch(kernel, dim3((dv + cols - 1) / cols, heads, num_requests), dim3(DELTA_THREADS), smem, stream, qk, v,
-                     g, beta, state, cu_q, state_slots, out, heads, kv_heads, dk, dv, lanes);
+                     g, beta, state, cu_q, state_slots, out, heads, kv_heads, dk, dv, lanes, tc);
 }
 }  // namespace
 

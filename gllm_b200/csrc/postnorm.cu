@@ -11,7 +11,7 @@
 namespace {
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 postnorm_add_rmsnorm_kernel(const T* __restrict__ value, const float* __restrict__ parts, int n_parts,
                             int64_t part_stride, const float* __restrict__ post_w, float post_eps,
                             const float* __restrict__ extra, float* __restrict__ resid, const float* __restrict__ w,
@@ -65,7 +65,9 @@ int postnorm_launch(const T* value, const float* parts, int n_parts, int64_t par
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return gllm_launch(postnorm_add_rmsnorm_kernel<T>, dim3(n_rows), dim3(256), smem, stream, value, parts, n_parts,
+  // few rows: a row's three passes are chains of loads, so more threads make each chain shorter
+  const int threads = n_rows <= 64 && hidden > 1024 ? 1024 : 256;
+  return gllm_launch(postnorm_add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, value, parts, n_parts,
                      part_stride, post_w, post_eps, extra, resid, w, eps, out, rows, n_rows, hidden);
 }
 }  // namespace
