@@ -25,54 +25,78 @@ constexpr int DELTA_MAX_TAPS = 16;
 
 // x [n, >= channels] at x_stride: the projections' output, q | k | v channels first (qk_cols = 2 * kv_heads * dk,
 // then heads * dv).  Outputs fp32: qk [n, qk_cols], v [n, heads * dv], g [n, heads * dk], beta [n, heads].
+// The work of a token is cut into units, one warp each: a q or k head (convolution, SiLU, unit norm: dk channels),
+// or a v head (dv channels) together with that head's decays and beta.  grid.y blocks share a token's units, so a
+// step of few tokens still fills the SMs.  `single` says that every request brings exactly one token: the thread
+// that read a channel's state then also shifts it and appends the token's input (no other token reads that state in
+// this step), and conv_state_update is not launched.
 template <typename T>
 __global__ void __launch_bounds__(256)
 delta_prep_kernel(const T* __restrict__ x, int64_t x_stride, const float* __restrict__ conv_w,
-                  const float* __restrict__ conv_state, const int* __restrict__ positions,
+                  float* conv_state, const int* __restrict__ positions,
                   const int* __restrict__ token_row, const float* __restrict__ a_raw, int64_t a_stride,
                   const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                   const float* __restrict__ b_raw, int64_t b_stride, float* __restrict__ qk, float* __restrict__ v,
                   float* __restrict__ g, float* __restrict__ beta, int heads, int kv_heads, int dk, int dv, int taps,
-                  float unit_eps, float q_scale) {
+                  float unit_eps, float q_scale, int single) {
   extern __shared__ float sm[];
   pdl_trigger();
   pdl_wait();
   const int i = blockIdx.x;
-  const int qk_cols = 2 * kv_heads * dk, channels = qk_cols + heads * dv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int qk_cols = 2 * kv_heads * dk, channels = qk_cols + heads * dv, units = 2 * kv_heads + heads;
   const int row = token_row[i], pos = positions[i];
   // how many of the request's earlier tokens this batch holds right before row i (at most taps-1 matter)
   int here = 0;
-  while (here < taps - 1 && i - here - 1 >= 0 && token_row[i - here - 1] == row && positions[i - here - 1] == pos - here - 1)
-    ++here;
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {          // j tokens back
-      float val;
-      if (j <= here) {
-        val = to_float(x[(int64_t)(i - j) * x_stride + c]);
-      } else {
-        const int idx = taps - 1 - (j - here);   // the state holds the inputs before the batch's first, oldest first
-        val = conv_state[((int64_t)row * (taps - 1) + idx) * channels + c];
-      }
-      acc = fmaf(conv_w[(int64_t)c * taps + (taps - 1 - j)], val, acc);
-    }
-    sm[c] = acc / (1.0f + expf(-acc));
-  }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int h = warp; h < 2 * kv_heads; h += nwarps) {
+  if (!single)
+    while (here < taps - 1 && i - here - 1 >= 0 && token_row[i - here - 1] == row && positions[i - here - 1] == pos - here - 1)
+      ++here;
+  float* mine = sm + warp * dk;
+  float* cs_row = conv_state + (int64_t)row * (taps - 1) * channels;
+  for (int u = blockIdx.y * nwarps + warp; u < units; u += gridDim.y * nwarps) {
+    const bool is_qk = u < 2 * kv_heads;
+    const int h = u - 2 * kv_heads;
+    const int c0 = is_qk ? u * dk : qk_cols + h * dv, width = is_qk ? dk : dv;
     float ss = 0.f;
-    for (int c = lane; c < dk; c += 32) ss = fmaf(sm[h * dk + c], sm[h * dk + c], ss);
-    ss = warp_sum(ss);
-    const float inv = (h < kv_heads ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
-    for (int c = lane; c < dk; c += 32) qk[(int64_t)i * qk_cols + h * dk + c] = sm[h * dk + c] * inv;
+    for (int c = lane; c < width; c += 32) {
+      const int ch = c0 + c;
+      const float* w = conv_w + (int64_t)ch * taps;
+      float acc = 0.f;
+      for (int j = 0; j < taps; ++j) {          // j tokens back
+        float val;
+        if (j <= here) {
+          val = to_float(x[(int64_t)(i - j) * x_stride + ch]);
+        } else {
+          const int idx = taps - 1 - (j - here);   // the state holds the inputs before the batch's first, oldest first
+          val = cs_row[(int64_t)idx * channels + ch];
+        }
+        acc = fmaf(w[taps - 1 - j], val, acc);
+      }
+      if (single && taps > 1) {
+        for (int j = 0; j + 2 < taps; ++j) cs_row[(int64_t)j * channels + ch] = cs_row[(int64_t)(j + 1) * channels + ch];
+        cs_row[(int64_t)(taps - 2) * channels + ch] = to_float(x[(int64_t)i * x_stride + ch]);
+      }
+      const float val = acc / (1.0f + expf(-acc));
+      if (is_qk) {
+        mine[c] = val;                          // read back below by the lane that wrote it
+        ss = fmaf(val, val, ss);
+      } else {
+        v[(int64_t)i * heads * dv + h * dv + c] = val;
+      }
+    }
+    if (is_qk) {
+      ss = warp_sum(ss);
+      const float inv = (u < kv_heads ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
+      for (int c = lane; c < dk; c += 32) qk[(int64_t)i * qk_cols + c0 + c] = mine[c] * inv;
+    } else {
+      const float rate = -expf(A_log[h]);
+      for (int c = lane; c < dk; c += 32) {
+        const int hc = h * dk + c;
+        g[(int64_t)i * heads * dk + hc] = expf(rate * softplusf_(a_raw[(int64_t)i * a_stride + hc] + dt_bias[hc]));
+      }
+      if (lane == 0) beta[(int64_t)i * heads + h] = sigmoidf_(b_raw[(int64_t)i * b_stride + h]);
+    }
   }
-  for (int c = threadIdx.x; c < heads * dv; c += blockDim.x) v[(int64_t)i * heads * dv + c] = sm[qk_cols + c];
-  for (int c = threadIdx.x; c < heads * dk; c += blockDim.x) {
-    const int h = c / dk;
-    g[(int64_t)i * heads * dk + c] = expf(-expf(A_log[h]) * softplusf_(a_raw[(int64_t)i * a_stride + c] + dt_bias[c]));
-  }
-  for (int h = threadIdx.x; h < heads; h += blockDim.x) beta[(int64_t)i * heads + h] = sigmoidf_(b_raw[(int64_t)i * b_stride + h]);
 }
 
 // conv_state [slots, taps-1, channels] <- the last taps-1 of (old state ++ this step's inputs), per request.
@@ -114,16 +138,16 @@ template <int N> __device__ __forceinline__ void copy_async_wait() {
 // reads four floats at a time, which needs dk and dv to be multiples of 4 (all row starts are then 16-byte aligned).
 // Per token the chain from state to state is: dot products with the decayed key and query (the decay is folded
 // into them, off the chain), their sums over the column's lanes, u, one fused multiply-add per state element.
-template <int DPT, int VEC>
+template <int DPT, int LANES, int VEC>
 __global__ void __launch_bounds__(DELTA_THREADS)
 delta_rule_kernel(const float* __restrict__ qk, const float* __restrict__ v, const float* __restrict__ g,
                   const float* __restrict__ beta, float* __restrict__ state, const int* __restrict__ cu_q,
                   const int* __restrict__ state_slots, float* __restrict__ out, int heads, int kv_heads, int dk,
-                  int dv, int lanes, int tc) {
+                  int dv, int tc) {
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   pdl_wait();
-  const int cols = DELTA_THREADS / lanes, dkp = lanes * DPT;
+  constexpr int lanes = LANES, cols = DELTA_THREADS / LANES, dkp = LANES * DPT;
   const int r = blockIdx.z, h = blockIdx.y, hg = h / (heads / kv_heads);
   const int cix = threadIdx.x / lanes, sub = threadIdx.x % lanes;
   const int col0 = blockIdx.x * cols, col = col0 + cix;
@@ -189,37 +213,68 @@ delta_rule_kernel(const float* __restrict__ qk, const float* __restrict__ v, con
     const float* vs = buf + 3 * tc * dkp + cix;
     const float* bs = buf + 3 * tc * dkp + tc * cols;
     float* op = out + ((int64_t)c0 * heads + h) * dv + col;
-    for (int t = 0; t < nt; ++t) {
-      float kk[DPT], gg[DPT];
-      float sk = 0.f, sq = 0.f, kq = 0.f;
+    // What a token brings (k, g, q, k.q summed over the lanes, v, beta) does not depend on the state and is fetched
+    // one token ahead, so that the chain from state to state is the decay, two dot products (in ACC partial sums
+    // each), their sums over the lanes, u and one fused multiply-add per element.
+    constexpr int ACC = DPT >= 16 ? 4 : (DPT >= 8 ? 2 : 1);
+    auto fetch = [&](int t, float (&k_)[DPT], float (&g_)[DPT], float (&q_)[DPT], float& kq_, float& v_, float& b_) {
       if (VEC == 4) {
 #pragma unroll
         for (int e = 0; e < DPT; e += 4) {
           const float4 a = *reinterpret_cast<const float4*>(ks + t * dkp + e);
           const float4 b = *reinterpret_cast<const float4*>(gs + t * dkp + e);
-          kk[e] = a.x, kk[e + 1] = a.y, kk[e + 2] = a.z, kk[e + 3] = a.w;
-          gg[e] = b.x, gg[e + 1] = b.y, gg[e + 2] = b.z, gg[e + 3] = b.w;
+          const float4 c = *reinterpret_cast<const float4*>(qs + t * dkp + e);
+          k_[e] = a.x, k_[e + 1] = a.y, k_[e + 2] = a.z, k_[e + 3] = a.w;
+          g_[e] = b.x, g_[e + 1] = b.y, g_[e + 2] = b.z, g_[e + 3] = b.w;
+          q_[e] = c.x, q_[e + 1] = c.y, q_[e + 2] = c.z, q_[e + 3] = c.w;
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < DPT; ++e) kk[e] = ks[t * dkp + e], gg[e] = gs[t * dkp + e];
+        for (int e = 0; e < DPT; ++e) k_[e] = ks[t * dkp + e], g_[e] = gs[t * dkp + e], q_[e] = qs[t * dkp + e];
       }
+      v_ = vs[t * cols];
+      b_ = bs[t];
+      float part[ACC] = {};
+#pragma unroll
+      for (int e = 0; e < DPT; ++e) part[e % ACC] = fmaf(k_[e], q_[e], part[e % ACC]);
+#pragma unroll
+      for (int w = ACC >> 1; w > 0; w >>= 1)
+#pragma unroll
+        for (int x = 0; x < w; ++x) part[x] += part[x + w];
+      kq_ = part[0];
+#pragma unroll
+      for (int o = LANES >> 1; o > 0; o >>= 1) kq_ += __shfl_xor_sync(0xffffffffu, kq_, o);
+    };
+    float kk[DPT], gg[DPT], qq[DPT], kq, vv, bb;
+    fetch(0, kk, gg, qq, kq, vv, bb);
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t) {
+      float nk[DPT], ng[DPT], nq[DPT], nkq, nv, nb;
+      fetch(min(t + 1, nt - 1), nk, ng, nq, nkq, nv, nb);
+      float pk[ACC] = {}, pq[ACC] = {};
 #pragma unroll
       for (int e = 0; e < DPT; ++e) {
-        const float qe = qs[t * dkp + e];
-        sk = fmaf(S[e], gg[e] * kk[e], sk);
-        sq = fmaf(S[e], gg[e] * qe, sq);
-        kq = fmaf(kk[e], qe, kq);
+        S[e] *= gg[e];
+        pk[e % ACC] = fmaf(S[e], kk[e], pk[e % ACC]);
+        pq[e % ACC] = fmaf(S[e], qq[e], pq[e % ACC]);
       }
-      for (int o = lanes >> 1; o > 0; o >>= 1) {
+#pragma unroll
+      for (int w = ACC >> 1; w > 0; w >>= 1)
+#pragma unroll
+        for (int x = 0; x < w; ++x) pk[x] += pk[x + w], pq[x] += pq[x + w];
+      float sk = pk[0], sq = pq[0];
+#pragma unroll
+      for (int o = LANES >> 1; o > 0; o >>= 1) {
         sk += __shfl_xor_sync(0xffffffffu, sk, o);
         sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        kq += __shfl_xor_sync(0xffffffffu, kq, o);
       }
-      const float u = bs[t] * (vs[t * cols] - sk);
+      const float u = bb * (vv - sk);
 #pragma unroll
-      for (int e = 0; e < DPT; ++e) S[e] = fmaf(kk[e], u, gg[e] * S[e]);
+      for (int e = 0; e < DPT; ++e) S[e] = fmaf(kk[e], u, S[e]);
       if (sub == 0 && live) op[(int64_t)t * heads * dv] = fmaf(u, kq, sq);
+#pragma unroll
+      for (int e = 0; e < DPT; ++e) kk[e] = nk[e], gg[e] = ng[e], qq[e] = nq[e];
+      kq = nkq, vv = nv, bb = nb;
     }
     __syncthreads();                                       // the next copies go into the buffer just read
   }
@@ -247,31 +302,45 @@ int delta_prep_launch(const T* x, int64_t x_stride, const float* conv_w, float* 
                       const int* token_row, const int* cu_q, const int* state_slots, int num_requests,
                       const float* a_raw, int64_t a_stride, const float* dt_bias, const float* A_log, const float* b_raw,
                       int64_t b_stride, float* qk, float* v, float* g, float* beta, int n_tokens, int heads, int kv_heads,
-                      int dk, int dv, int taps, float unit_eps, float q_scale, cudaStream_t stream) {
+                      int dk, int dv, int taps, float unit_eps, float q_scale, int max_q_len, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  const int channels = 2 * kv_heads * dk + heads * dv;
-  const size_t smem = sizeof(float) * (size_t)channels;
-  if (taps < 1 || taps > DELTA_MAX_TAPS || heads % kv_heads || smem > 200 * 1024 || num_requests > 65535)
+  const int channels = 2 * kv_heads * dk + heads * dv, units = 2 * kv_heads + heads, nwarps = 8;
+  const size_t smem = sizeof(float) * (size_t)nwarps * dk;
+  if (taps < 1 || taps > DELTA_MAX_TAPS || heads % kv_heads || smem > 48 * 1024 || num_requests > 65535)
     return (int)cudaErrorInvalidValue;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
-  int rc = gllm_launch(delta_prep_kernel<T>, dim3(n_tokens), dim3(256), smem, stream, x, x_stride, conv_w,
-                       (const float*)conv_state, positions, token_row, a_raw, a_stride, dt_bias, A_log, b_raw, b_stride,
-                       qk, v, g, beta, heads, kv_heads, dk, dv, taps, unit_eps, q_scale);
-  if (rc != 0 || taps == 1 || num_requests <= 0) return rc;
+  // a token's units spread over as many blocks as it takes to give every SM a few, at most one unit a warp
+  int parts = (4 * 148 + n_tokens - 1) / n_tokens;
+  parts = std::max(1, std::min(parts, (units + nwarps - 1) / nwarps));
+  const int single = max_q_len == 1 && n_tokens == num_requests;
+  int rc = gllm_launch(delta_prep_kernel<T>, dim3(n_tokens, parts), dim3(32 * nwarps), smem, stream, x, x_stride, conv_w,
+                       conv_state, positions, token_row, a_raw, a_stride, dt_bias, A_log, b_raw, b_stride,
+                       qk, v, g, beta, heads, kv_heads, dk, dv, taps, unit_eps, q_scale, single);
+  if (rc != 0 || taps == 1 || num_requests <= 0 || single) return rc;
   return gllm_launch(conv_state_update_kernel<T>, dim3((channels + 255) / 256, num_requests), dim3(256), 0, stream, x,
                      x_stride, conv_state, cu_q, state_slots, channels, taps);
 }
 
 int delta_rule_launch(const float* qk, const float* v, const float* g, const float* beta, float* state,
                       const int* cu_q, const int* state_slots, float* out, int num_requests, int heads, int kv_heads,
-                      int dk, int dv, cudaStream_t stream) {
+                      int dk, int dv, int max_q_len, cudaStream_t stream) {
   if (num_requests <= 0) return 0;
   if (heads > 65535 || num_requests > 65535 || dk < 1 || dv < 1 || dk > 512 || heads % kv_heads)
     return (int)cudaErrorInvalidValue;
-  const int dpt = dk <= 128 ? 4 : (dk <= 256 ? 8 : 16);
+  // Key channels a thread keeps (DPT).  More of them mean fewer threads a column, so fewer rounds of shuffles and more
+  // independent work per warp, but fewer warps in all.  Measured: four for heads of up to 64 key channels and eight
+  // beyond when one prompt runs alone (every warp the step can have is wanted); eight when every request brings one
+  // token (the step is then bound by reading and writing the states); thirty-two for several prompts at once, as soon
+  // as that still gives every SM its blocks.
+  int dpt = dk <= 128 ? 4 : (dk <= 256 ? 8 : 16);
+  if (dk % 4 == 0) {
+    dpt = dk <= 64 ? 4 : (dk <= 256 ? 8 : 16);
+    if (dk <= 64 && max_q_len == 1) dpt = std::min(8, std::max(4, dk));
+    if (dk > 32 && dk <= 64 && max_q_len != 1 && (int64_t)((dv + 63) / 64) * heads * num_requests >= 240) dpt = 32;
+  }
+  if (const char* e = getenv("GLLM_B200_DELTA_DPT")) {
+    const int want = atoi(e);
+    if ((want == 4 || want == 8 || want == 16 || want == 32) && want * 32 >= dk && dk % 4 == 0) dpt = want;
+  }
   const int lanes = pow2_at_least((dk + dpt - 1) / dpt);
   const int cols = DELTA_THREADS / lanes, dkp = lanes * dpt;
   int tc = DELTA_MAX_CHUNK;
@@ -281,16 +350,40 @@ int delta_rule_launch(const float* qk, const float* v, const float* g, const flo
                    ((reinterpret_cast<uintptr_t>(qk) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(g) |
                      reinterpret_cast<uintptr_t>(state)) & 15) == 0;
   using Kernel = void (*)(const float*, const float*, const float*, const float*, float*, const int*, const int*, float*,
-                          int, int, int, int, int, int);
-  Kernel kernel = dpt == 4 ? (vec ? delta_rule_kernel<4, 4> : delta_rule_kernel<4, 1>)
-                           : (dpt == 8 ? (vec ? delta_rule_kernel<8, 4> : delta_rule_kernel<8, 1>)
-                                       : (vec ? delta_rule_kernel<16, 4> : delta_rule_kernel<16, 1>));
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                          int, int, int, int, int);
+  Kernel kernel = nullptr;
+#define GLLM_DELTA_PICK(D, L) \
+  if (dpt == D && lanes == L) kernel = vec ? delta_rule_kernel<D, L, 4> : delta_rule_kernel<D, L, 1>;
+#define GLLM_DELTA_PICK4(D, L) \
+  if (dpt == D && lanes == L && vec) kernel = delta_rule_kernel<D, L, 4>;
+  GLLM_DELTA_PICK(4, 1) GLLM_DELTA_PICK(4, 2) GLLM_DELTA_PICK(4, 4) GLLM_DELTA_PICK(4, 8) GLLM_DELTA_PICK(4, 16)
+  GLLM_DELTA_PICK(4, 32) GLLM_DELTA_PICK(8, 32) GLLM_DELTA_PICK(16, 32)
+  GLLM_DELTA_PICK4(8, 1) GLLM_DELTA_PICK4(8, 2) GLLM_DELTA_PICK4(8, 4) GLLM_DELTA_PICK4(8, 8) GLLM_DELTA_PICK4(8, 16)
+  GLLM_DELTA_PICK4(16, 1) GLLM_DELTA_PICK4(16, 2) GLLM_DELTA_PICK4(16, 4) GLLM_DELTA_PICK4(16, 8) GLLM_DELTA_PICK4(16, 16)
+  GLLM_DELTA_PICK4(32, 1) GLLM_DELTA_PICK4(32, 2) GLLM_DELTA_PICK4(32, 4) GLLM_DELTA_PICK4(32, 8) GLLM_DELTA_PICK4(32, 16)
+#undef GLLM_DELTA_PICK4
+#undef GLLM_DELTA_PICK
+  if (kernel == nullptr) return (int)cudaErrorInvalidValue;
+  // The kernel is bound by the latency of each warp's chain, so its blocks should lie evenly over the SMs.  A block
+  // that starts while the kernel before it drains lands wherever a place frees first; asking for a share of an SM's
+  // shared memory that lets no SM take more than its even share of the blocks keeps them spread.
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+      sm_count = 148;
+  }
+  const int64_t blocks = (int64_t)((dv + cols - 1) / cols) * heads * num_requests;
+  const int64_t per_sm = (blocks + sm_count - 1) / sm_count;
+  const size_t share = (size_t)(228 * 1024 / per_sm) - 1024;     // 1 KB of every block's share is the system's
+  const size_t smem_ask = std::max(smem, std::min(share, (size_t)227 * 1024));
+  if (smem_ask > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
   }
-  return gllm_launch(kernel, dim3((dv + cols - 1) / cols, heads, num_requests), dim3(DELTA_THREADS), smem, stream, qk, v,
-                     g, beta, state, cu_q, state_slots, out, heads, kv_heads, dk, dv, lanes, tc);
+  return gllm_launch(kernel, dim3((dv + cols - 1) / cols, heads, num_requests), dim3(DELTA_THREADS), smem_ask, stream, qk, v,
+                     g, beta, state, cu_q, state_slots, out, heads, kv_heads, dk, dv, tc);
 }
 }  // namespace
 
@@ -300,10 +393,11 @@ int delta_rule_launch(const float* qk, const float* v, const float* g, const flo
                                    const int* state_slots, int num_requests, const float* a_raw, int64_t a_stride,     \
                                    const float* dt_bias, const float* A_log, const float* b_raw, int64_t b_stride,     \
                                    float* qk, float* v, float* g, float* beta, int n_tokens, int heads, int kv_heads,  \
-                                   int dk, int dv, int taps, float unit_eps, float q_scale, cudaStream_t stream) {     \
+                                   int dk, int dv, int taps, float unit_eps, float q_scale, int max_q_len,             \
+                                   cudaStream_t stream) {                                                              \
     return delta_prep_launch<T>(x, x_stride, conv_w, conv_state, positions, token_row, cu_q, state_slots,              \
                                 num_requests, a_raw, a_stride, dt_bias, A_log, b_raw, b_stride, qk, v, g, beta,        \
-                                n_tokens, heads, kv_heads, dk, dv, taps, unit_eps, q_scale, stream);                   \
+                                n_tokens, heads, kv_heads, dk, dv, taps, unit_eps, q_scale, max_q_len, stream);        \
   }
 GLLM_DELTA_EXPORTS(float, f32)
 GLLM_DELTA_EXPORTS(__nv_bfloat16, bf16)
@@ -311,6 +405,6 @@ GLLM_DELTA_EXPORTS(__nv_bfloat16, bf16)
 GLLM_API int gllm_delta_rule(const float* qk, const float* v, const float* g, const float* beta, float* state,
                              const int* cu_q, const int* state_slots, float* out, int num_requests, int heads,
                              int kv_heads, int dk, int dv, int max_q_len, cudaStream_t stream) {
-  (void)max_q_len;
-  return delta_rule_launch(qk, v, g, beta, state, cu_q, state_slots, out, num_requests, heads, kv_heads, dk, dv, stream);
+  return delta_rule_launch(qk, v, g, beta, state, cu_q, state_slots, out, num_requests, heads, kv_heads, dk, dv, max_q_len,
+                           stream);
 }

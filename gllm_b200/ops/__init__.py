@@ -113,7 +113,7 @@ _SIGNATURES = {
     },
     "delta_rule": {
         "gllm_delta_prep_{t}": [P, c_int64, P, P, P, P, P, P, c_int, P, c_int64, P, P, P, c_int64, P, P, P, P, c_int,
-                                c_int, c_int, c_int, c_int, c_int, c_float, c_float, P],
+                                c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, P],
         "gllm_delta_rule": [P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
     },
     "moe": {

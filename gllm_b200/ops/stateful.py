@@ -226,7 +226,7 @@ def head_norm(o: torch.Tensor, heads: int, dv: int, weight: torch.Tensor, eps: f
 def delta_prep(x: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Tensor, positions: torch.Tensor,
                token_row: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, num_requests: int,
                decay_raw: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, beta_raw: torch.Tensor, heads: int,
-               kv_heads: int, dk: int, dv: int, unit_eps: float, q_scale: float):
+               kv_heads: int, dk: int, dv: int, unit_eps: float, q_scale: float, max_q_len: int = 0):
     """What the delta rule's recurrence takes, in fp32, from the projections of a step's tokens.
 
     ``x [n, >= channels]`` (rows may be slices): the q | k | v projections (``token_row``: each token's state slot), ``channels = 2 * kv_heads * dk +
@@ -235,7 +235,8 @@ def delta_prep(x: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Ten
     every request's last inputs, oldest first, and is brought up to date) and SiLU; every q and k head becomes
     ``x / sqrt(sum(x^2) + unit_eps)``, q also times ``q_scale``.  ``decay_raw [n, heads * dk]`` and ``beta_raw
     [n, heads]`` are fp32: ``g = exp(-exp(A_log[h]) * softplus(decay_raw + dt_bias))``, ``beta = sigmoid(beta_raw)``.
-    Returns ``(qk [n, 2 * kv_heads * dk], v [n, heads * dv], g [n, heads * dk], beta [n, heads])``."""
+    ``max_q_len`` 1 says that every request brings one token: the state is then brought up to date by the same
+    kernel.  Returns ``(qk [n, 2 * kv_heads * dk], v [n, heads * dv], g [n, heads * dk], beta [n, heads])``."""
     _rows(x, "x")
     _rows(decay_raw, "decay_raw", torch.float32)
     _rows(beta_raw, "beta_raw", torch.float32)
@@ -258,7 +259,7 @@ def delta_prep(x: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Ten
              token_row.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(), int(num_requests), decay_raw.data_ptr(),
              decay_raw.stride(0), dt_bias.data_ptr(), A_log.data_ptr(), beta_raw.data_ptr(), beta_raw.stride(0),
              qk.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), n, heads, kv_heads, dk, dv, taps,
-             float(unit_eps), float(q_scale), _stream()), "delta_prep")
+             float(unit_eps), float(q_scale), int(max_q_len), _stream()), "delta_prep")
     return qk, v, g, beta
 
 

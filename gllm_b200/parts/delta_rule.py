@@ -114,7 +114,7 @@ class GatedDeltaRule(Mixer):
         qk, v, g, beta = stateful.delta_prep(proj, self.conv, conv_state, ctx.positions, ctx.token_row, ctx.cu_q,
                                              ctx.state_slots, ctx.num_requests, decay_raw, self.dt_bias, self.A_log,
                                              beta_raw, self.heads, self.kv_heads, self.dk, self.dv, self.unit_eps,
-                                             self.q_scale)
+                                             self.q_scale, max_q_len=ctx.max_q_len)
         o = stateful.delta_rule(qk, v, g, beta, memory, ctx.cu_q, ctx.state_slots, ctx.num_requests, self.heads,
                                 self.kv_heads, self.dk, self.dv, max_q_len=ctx.max_q_len)
         normed = stateful.head_norm(o, self.heads, self.dv, self.norm, self.eps, x.dtype, gate=gate)
