@@ -189,22 +189,26 @@ def decode_step(batch=8, context=2048, layers=2, iters=3, peaks=None):
     return {"kernel": "decode_step (no graph)", "us": round(us, 2), "shape": dict(batch=batch, context=context, layers=layers)}
 
 
-def add_rmsnorm(rows=8, hidden=2048, splits=8, iters=5, peaks=None):
+def add_rmsnorm(rows=8, hidden=2048, splits=8, post=0, iters=5, peaks=None):
     """resid += (sum of ``splits`` fp32 partial products, 0: a summed bf16 branch), then RMSNorm: the
-    kernel between two products of a layer."""
+    kernel between two products of a layer.  ``post``: the branch is RMS-normed with a weight of its own
+    before it is added (the norm after a sublayer of a layer that norms both sides of it)."""
     from gllm_b200 import ops
 
     resid = torch.randn(rows, hidden, device="cuda")
     weight = torch.ones(hidden, device="cuda")
     parts = torch.randn(max(splits, 1), rows, hidden, device="cuda")
     branch = ops.SplitSum(parts, torch.bfloat16) if splits else parts[0].to(torch.bfloat16)
+    if post:
+        branch = ops.Pending(branch, torch.ones(hidden, device="cuda"), 1e-5)
     out = torch.empty(rows, hidden, dtype=torch.bfloat16, device="cuda")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     us = _time(lambda: ops.add_rmsnorm(branch, resid, weight, 1e-5, torch.bfloat16, out=out), iters, flush)
-    nbytes = rows * hidden * ((4 * splits if splits else 2) + 4 + 4 + 2) + hidden * 4
+    nbytes = rows * hidden * ((4 * splits if splits else 2) + 4 + 4 + 2) + hidden * 4 * (2 if post else 1)
     gbs = nbytes / us / 1e3
-    return {"kernel": "add_rmsnorm", "us": round(us, 2), "bytes": nbytes, "achieved_gbs": round(gbs, 1),
-            "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4), "shape": dict(rows=rows, hidden=hidden, splits=splits)}
+    return {"kernel": "add_rmsnorm (normed branch)" if post else "add_rmsnorm", "us": round(us, 2), "bytes": nbytes,
+            "achieved_gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4),
+            "shape": dict(rows=rows, hidden=hidden, splits=splits)}
 
 
 def argmax(rows=8, vocab=128256, iters=5, peaks=None):
