@@ -82,15 +82,29 @@ def _batch(lengths, starts, slots):
 
 
 @pytest.mark.parametrize("heads,kv_heads,dk,dv,taps", [(4, 2, 16, 8, 3), (3, 1, 10, 6, 1), (2, 2, 64, 64, 4),
-                                                      (1, 1, 20, 12, 2), (6, 3, 32, 40, 3)])
+                                                      (1, 1, 20, 12, 2), (6, 3, 32, 40, 3), (2, 1, 128, 32, 4),
+                                                      (1, 1, 320, 16, 2), (2, 2, 36, 20, 3), (60, 30, 64, 128, 2)])
 def test_delta_rule_kernels(heads, kv_heads, dk, dv, taps):
-    """The convolution, unit norms, decay and the recurrence over two requests in two steps (a portion each, then a
-    portion beside a single token), on state slots that are not the requests' numbers, against the plain functions."""
+    """The convolution, unit norms, decay and the recurrence over two requests in three steps (a portion each, then a
+    portion beside a single token, then a single token each), on state slots that are not the requests' numbers,
+    against the plain functions.  The sizes reach every number of key channels per thread the kernel picks by itself
+    (few and many blocks, heads of 10 to 320 key channels, single tokens only)."""
+    _delta_rule_case(heads, kv_heads, dk, dv, taps)
+
+
+@pytest.mark.parametrize("channels_per_thread", [4, 8, 16, 32])
+def test_delta_rule_every_thread_layout(channels_per_thread, monkeypatch):
+    """The same recurrence with 4, 8, 16 and 32 key channels per thread (the kernel reads the choice at every launch)."""
+    monkeypatch.setenv("GLLM_B200_DELTA_DPT", str(channels_per_thread))
+    _delta_rule_case(2, 1, 64, 48, 3)
+
+
+def _delta_rule_case(heads, kv_heads, dk, dv, taps):
     from gllm_b200.ops import stateful
 
     g = torch.Generator().manual_seed(heads * 100 + dk)
     qk_cols, channels = 2 * kv_heads * dk, 2 * kv_heads * dk + heads * dv
-    total = {0: 21, 1: 9}
+    total = {0: 22, 1: 10}
     x = {r: torch.randn(n, channels, generator=g) for r, n in total.items()}
     raw = {r: torch.randn(n, heads * dk, generator=g) * 2 for r, n in total.items()}
     braw = {r: torch.randn(n, heads, generator=g) * 2 for r, n in total.items()}
@@ -122,14 +136,14 @@ def test_delta_rule_kernels(heads, kv_heads, dk, dv, taps):
         conv_state[s] = 0
     got = {r: [] for r in total}
     done = {0: 0, 1: 0}
-    for plan in ([(0, 13), (1, 8)], [(1, 1), (0, 8)]):
+    for plan in ([(0, 13), (1, 8)], [(1, 1), (0, 8)], [(0, 1), (1, 1)]):
         lengths = [n for _, n in plan]
         cu, pos, row = _batch(lengths, [done[r] for r, _ in plan], [slot_of[r] for r, _ in plan])
         cat = lambda d: torch.cat([d[r][done[r]:done[r] + n] for r, n in plan]).cuda().contiguous()
         ss = torch.tensor([slot_of[r] for r, _ in plan], dtype=torch.int32, device="cuda")
         qk, v, dec, beta = stateful.delta_prep(cat(x), conv_w.cuda(), conv_state, pos, row, cu, ss, len(plan), cat(raw),
                                                dt_bias.cuda(), A_log.cuda(), cat(braw), heads, kv_heads, dk, dv,
-                                               unit_eps, q_scale)
+                                               unit_eps, q_scale, max_q_len=max(lengths))
         o = stateful.delta_rule(qk, v, dec, beta, state, cu, ss, len(plan), heads, kv_heads, dk, dv,
                                 max_q_len=max(lengths))
         at = 0
