@@ -533,7 +533,7 @@ GLLM_API int gllm_sum_parts_bf16(const float* parts, int n_parts, int64_t part_s
 // same features (the layout the gated product's weight uses).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter,
-                                int block) {
+                                int block, const float* __restrict__ bias) {
   pdl_trigger();
   pdl_wait();
   const size_t total = (size_t)n_rows * inter;
@@ -541,8 +541,12 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t r = idx / inter, c = idx - r * inter;
     const size_t gc = block ? (c / block) * 2 * block + c % block : c;
-    const float g = to_float(gate_up[r * 2 * inter + gc]);
-    const float u = to_float(gate_up[r * 2 * inter + gc + (block ? block : inter)]);
+    float g = to_float(gate_up[r * 2 * inter + gc]);
+    float u = to_float(gate_up[r * 2 * inter + gc + (block ? block : inter)]);
+    if (bias != nullptr) {                       // rounded to T as a product with a bias leaves its result
+      g = to_float(from_float<T>(g + bias[gc]));
+      u = to_float(from_float<T>(u + bias[gc + (block ? block : inter)]));
+    }
     const float s = g / (1.0f + expf(-g));
     out[idx] = from_float<T>(s * u);
   }
@@ -550,7 +554,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 
 template <typename T>
 __global__ void silu_mul_wide_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter,
-                                     int block) {
+                                     int block, const float* __restrict__ bias) {
   pdl_trigger();
   pdl_wait();
   const int per_row = inter / 8;
@@ -563,6 +567,13 @@ __global__ void silu_mul_wide_kernel(const T* __restrict__ gate_up, T* __restric
     const int gc = block ? (c / block) * 2 * block + c % block : c;
     Vec8<T>::load(gate_up + r * 2 * inter + gc, g);
     Vec8<T>::load(gate_up + r * 2 * inter + gc + (block ? block : inter), u);
+    if (bias != nullptr) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        g[e] = to_float(from_float<T>(g[e] + bias[gc + e]));
+        u[e] = to_float(from_float<T>(u[e] + bias[gc + (block ? block : inter) + e]));
+      }
+    }
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
     Vec8<T>::store(out + r * inter + c, y);
@@ -570,7 +581,8 @@ __global__ void silu_mul_wide_kernel(const T* __restrict__ gate_up, T* __restric
 }
 
 template <typename T>
-static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, int block, cudaStream_t stream) {
+static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, int block, const float* bias,
+                           cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (block < 0 || (block > 0 && inter % block)) return (int)cudaErrorInvalidValue;
   if (inter % 8 == 0 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
@@ -578,20 +590,20 @@ static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, int 
     int wide_blocks = (int)((chunks + 255) / 256);
     if (wide_blocks > gllm_sm_count() * 16) wide_blocks = gllm_sm_count() * 16;
     return gllm_launch(silu_mul_wide_kernel<T>, dim3(wide_blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter,
-                       block);
+                       block, bias);
   }
   const size_t total = (size_t)n_rows * inter;
   int blocks = (int)((total + 255) / 256);
   if (blocks > gllm_sm_count() * 16) blocks = gllm_sm_count() * 16;
-  return gllm_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter, block);
+  return gllm_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter, block, bias);
 }
-GLLM_API int gllm_silu_mul_f32(const float* gate_up, float* out, int n_rows, int inter, int block,
+GLLM_API int gllm_silu_mul_f32(const float* gate_up, float* out, int n_rows, int inter, int block, const float* bias,
                                cudaStream_t stream) {
-  return silu_mul_launch<float>(gate_up, out, n_rows, inter, block, stream);
+  return silu_mul_launch<float>(gate_up, out, n_rows, inter, block, bias, stream);
 }
 GLLM_API int gllm_silu_mul_bf16(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int n_rows, int inter, int block,
-                                cudaStream_t stream) {
-  return silu_mul_launch<__nv_bfloat16>(gate_up, out, n_rows, inter, block, stream);
+                                const float* bias, cudaStream_t stream) {
+  return silu_mul_launch<__nv_bfloat16>(gate_up, out, n_rows, inter, block, bias, stream);
 }
 
 // ------------------------------------------- rotary positions + cache store

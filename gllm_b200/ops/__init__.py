@@ -61,7 +61,7 @@ _SIGNATURES = {
         "gllm_rmsnorm_heads_{t}": [P, c_int64, P, c_int, c_int, c_int, c_int, c_float, c_int, P],
         "gllm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_float, c_int, P],
         "gllm_sum_parts_{t}": [P, c_int, c_int64, P, c_int64, P],
-        "gllm_silu_mul_{t}": [P, P, c_int, c_int, c_int, P],
+        "gllm_silu_mul_{t}": [P, P, c_int, c_int, c_int, P, P],
         "gllm_relu_sq_{t}": [P, P, c_int64, P],
         "gllm_scaled_sum_{t}": [P, P, P, c_float, c_float, c_int64, P],
         "gllm_gated_act_{t}": [P, P, c_int, c_int, c_int, c_float, c_float, c_float, P],
@@ -529,10 +529,16 @@ def _pending_add_rmsnorm(pending: Pending, resid, weight, eps, out_dtype, rows, 
 GATED_BLOCK = 64
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int = 0) -> torch.Tensor:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int = 0,
+             bias: torch.Tensor | None = None) -> torch.Tensor:
     """``silu(gate) * up`` of ``[n, 2*inter]``.  ``block`` 0: gate columns first, up columns after;
-    ``block`` b: b gate columns alternate with the b up columns of the same features."""
+    ``block`` b: b gate columns alternate with the b up columns of the same features.  ``bias`` (fp32, one value per
+    column of ``gate_up``) is added first, with the rounding a product with a bias gives its result."""
     _cuda(gate_up, "gate_up")
+    if bias is not None:
+        _cuda(bias, "bias", torch.float32)
+        if bias.numel() != gate_up.shape[1]:
+            raise ValueError("one bias value per column of gate_up is needed")
     n, two_i = gate_up.shape
     if two_i % 2:
         raise ValueError("gate_up must have an even number of columns")
@@ -540,7 +546,7 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int 
     if out is None:
         out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
     f = _fn("elementwise", f"gllm_silu_mul_{_suffix(gate_up.dtype)}")
-    _check(f(gate_up.data_ptr(), out.data_ptr(), n, inter, int(block), _stream()), "silu_mul")
+    _check(f(gate_up.data_ptr(), out.data_ptr(), n, inter, int(block), _ptr(bias), _stream()), "silu_mul")
     return out
 
 

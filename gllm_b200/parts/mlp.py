@@ -61,7 +61,7 @@ class SwiGLU(FeedForward):
         if self.gated_blocks:
             hidden = ops.linear_gated(x, self.w_gate_up)
         else:
-            hidden = ops.silu_mul(ops.linear(x, self.w_gate_up, bias=self.b_gate_up))
+            hidden = ops.silu_mul(ops.linear(x, self.w_gate_up), bias=self.b_gate_up)
         return ops.linear(hidden, self.w_down, split_ok=True, add_into=sink, bias=self.b_down)
 
 

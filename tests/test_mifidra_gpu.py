@@ -158,6 +158,25 @@ def _delta_rule_case(heads, kv_heads, dk, dv, taps):
     assert float(state[0].min()) == 7.0 and (taps == 1 or float(conv_state[4].min()) == 7.0)   # others: untouched
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,inter", [(5, 24), (3, 20), (70, 64)])
+def test_activation_with_the_gate_and_up_biases(dtype, rows, inter):
+    """``silu(gate + b_g) * (up + b_u)`` in one kernel gives what the bias kernel followed by the activation gives, bit
+    for bit, and what the plain formula gives."""
+    from gllm_b200 import ops
+
+    g = torch.Generator().manual_seed(rows * inter)
+    x = torch.randn(rows, 2 * inter, generator=g).to(dtype).cuda()
+    bias = torch.randn(2 * inter, generator=g).cuda()
+    fused = ops.silu_mul(x, bias=bias)
+    two_steps = ops.silu_mul(ops.add_bias(x.clone(), bias))
+    assert torch.equal(fused, two_steps)
+    y = (x.double() + bias.double()).cpu()
+    want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert torch.allclose(fused.double().cpu(), want, rtol=tol, atol=tol)
+
+
 @pytest.mark.parametrize("experts,top,groups,keep", [(16, 6, 4, 2), (8, 2, 4, 2), (6, 3, 1, 1), (4, 1, 4, 2),
                                                       (12, 5, 3, 2), (64, 8, 8, 4), (5, 5, 1, 1)])
 def test_router_kernel(experts, top, groups, keep):
