@@ -331,24 +331,25 @@ int delta_rule_launch(const float* qk, const float* v, const float* g, const flo
   // beyond when one prompt runs alone (every warp the step can have is wanted); eight when every request brings one
   // token (the step is then bound by reading and writing the states); thirty-two for several prompts at once, as soon
   // as that still gives every SM its blocks.
+  // copies and loads of four floats at a time want every row start on a 16-byte boundary
+  const bool vec = dk % 4 == 0 && dv % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(qk) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(g) |
+                     reinterpret_cast<uintptr_t>(state)) & 15) == 0;
   int dpt = dk <= 128 ? 4 : (dk <= 256 ? 8 : 16);
-  if (dk % 4 == 0) {
+  if (vec) {
     dpt = dk <= 64 ? 4 : (dk <= 256 ? 8 : 16);
     if (dk <= 64 && max_q_len == 1) dpt = std::min(8, std::max(4, dk));
     if (dk > 32 && dk <= 64 && max_q_len != 1 && (int64_t)((dv + 63) / 64) * heads * num_requests >= 240) dpt = 32;
   }
   if (const char* e = getenv("GLLM_B200_DELTA_DPT")) {
     const int want = atoi(e);
-    if ((want == 4 || want == 8 || want == 16 || want == 32) && want * 32 >= dk && dk % 4 == 0) dpt = want;
+    if ((want == 4 || want == 8 || want == 16 || want == 32) && want * 32 >= dk && vec) dpt = want;
   }
   const int lanes = pow2_at_least((dk + dpt - 1) / dpt);
   const int cols = DELTA_THREADS / lanes, dkp = lanes * dpt;
   int tc = DELTA_MAX_CHUNK;
   while (tc > 2 && 2 * tc * (3 * dkp + cols + 1) * sizeof(float) > 96 * 1024) tc >>= 1;
   const size_t smem = sizeof(float) * 2 * (size_t)((tc * (3 * dkp + cols + 1) + 3) & ~3);
-  const bool vec = dk % 4 == 0 && dv % 4 == 0 &&
-                   ((reinterpret_cast<uintptr_t>(qk) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(g) |
-                     reinterpret_cast<uintptr_t>(state)) & 15) == 0;
   using Kernel = void (*)(const float*, const float*, const float*, const float*, float*, const int*, const int*, float*,
                           int, int, int, int, int);
   Kernel kernel = nullptr;

@@ -83,7 +83,8 @@ def _batch(lengths, starts, slots):
 
 @pytest.mark.parametrize("heads,kv_heads,dk,dv,taps", [(4, 2, 16, 8, 3), (3, 1, 10, 6, 1), (2, 2, 64, 64, 4),
                                                       (1, 1, 20, 12, 2), (6, 3, 32, 40, 3), (2, 1, 128, 32, 4),
-                                                      (1, 1, 320, 16, 2), (2, 2, 36, 20, 3), (60, 30, 64, 128, 2)])
+                                                      (1, 1, 320, 16, 2), (2, 2, 36, 20, 3), (60, 30, 64, 128, 2), (2, 1, 16, 10, 2),
+                                                      (3, 3, 64, 6, 3)])
 def test_delta_rule_kernels(heads, kv_heads, dk, dv, taps):
     """The convolution, unit norms, decay and the recurrence over two requests in three steps (a portion each, then a
     portion beside a single token, then a single token each), on state slots that are not the requests' numbers,
