@@ -39,6 +39,7 @@ def _ensure_builtin_loaded() -> None:
     import gllm_b200.models.llama  # noqa: F401
     import gllm_b200.models.mifidra  # noqa: F401
     import gllm_b200.models.rulunex  # noqa: F401
+    import gllm_b200.models.sazisun  # noqa: F401
 
 
 def architecture_for(name: str) -> Architecture:

@@ -1,16 +1,19 @@
-// Routed experts: every token is served by `top` of `experts` small gated feed-forwards.
-//   moe_route    per token (one warp): scores s = sigmoid(z) of the fp32 router logits; the choice is made on
+// Routed experts: every token is served by `top` of `experts` small feed-forwards.
+//   moe_route    per token (one warp): scores s = sigmoid(z) of the fp32 router logits, or softmax(z) over all
+//                experts (`softmax_scores`); the choice is made on
 //                s + correction, optionally only among the experts of the `keep` best of `groups` equal groups of
-//                neighbours (a group's score: the sum of its two largest choice scores; experts of other groups
-//                count as minus infinity); the weights are the chosen experts' s (divided by their sum with
-//                `renorm`).  Ties go to the lower index.
+//                neighbours (a group's score: the sum of its two largest choice scores, or its largest alone with
+//                `group_max`; experts of other groups
+//                count as minus infinity); the weights are the chosen experts' s (divided by their sum + renorm_eps with
+//                `renorm`), times `weight_scale`.  Ties go to the lower index.
 //   moe_align    (one block) sorts the (token, slot) pairs by expert: every expert's pairs form whole tiles of
 //                `tile_m` rows (the last one filled up with -1), so that a tile of the products below reads ONE
 //                expert's weights; writes the pair of every row, the expert of every tile and the tile count.
 //   moe_gemm     out[pair] = A[row of pair] @ W[expert]^T over the tiles; `gated`: W holds gate and up rows and
-//                the result is silu(gate) * up, rounded to T; otherwise the fp32 result itself.
+//                the result is silu(gate) * up, rounded to T; `act` 1 (experts without a gate): the square of
+//                max(result, 0), rounded to T; otherwise the fp32 result itself.
 //   moe_combine  out[token] = sum over its slots, in slot order, of weight * result[pair] (+ a shared expert's
-//                result), rounded to T.
+//                result, times sigmoid(shared_gate[token]) when the shared expert has a gate), rounded to T.
 // A pair's result does not depend on which other pairs share its tile or on the tile's place: every row is a dot
 // product over K in one fixed order.  Scores, choice, weights, accumulators and the combination are fp32.
 #include "common.cuh"
@@ -33,7 +36,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 __global__ void __launch_bounds__(32)
 moe_route_kernel(const float* __restrict__ logits, int64_t stride, const float* __restrict__ correction,
                  int* __restrict__ ids, float* __restrict__ weights, int experts, int top, int groups, int keep,
-                 int renorm) {
+                 int renorm, int softmax_scores, int group_max, float renorm_eps, float weight_scale) {
   extern __shared__ float sm[];
   float* s = sm;                 // [experts] scores
   float* c = s + experts;        // [experts] choice scores
@@ -41,9 +44,20 @@ moe_route_kernel(const float* __restrict__ logits, int64_t stride, const float* 
   pdl_trigger();
   pdl_wait();
   const int i = blockIdx.x, lane = threadIdx.x;
+  float z_max = -CUDART_INF_F, z_sum = 0.f;
+  if (softmax_scores) {
+    for (int e = lane; e < experts; e += 32) z_max = fmaxf(z_max, logits[(int64_t)i * stride + e]);
+    z_max = warp_max(z_max);
+    for (int e = lane; e < experts; e += 32) {
+      const float v = expf(logits[(int64_t)i * stride + e] - z_max);
+      s[e] = v;
+      z_sum += v;
+    }
+    z_sum = warp_sum(z_sum);
+  }
   for (int e = lane; e < experts; e += 32) {
     const float z = logits[(int64_t)i * stride + e];
-    const float v = 1.0f / (1.0f + expf(-z));
+    const float v = softmax_scores ? s[e] / z_sum : 1.0f / (1.0f + expf(-z));
     s[e] = v;
     c[e] = v + (correction ? correction[e] : 0.f);
   }
@@ -61,7 +75,7 @@ moe_route_kernel(const float* __restrict__ logits, int64_t stride, const float* 
           m2 = v;
         }
       }
-      gs[g] = per > 1 ? m1 + m2 : m1;
+      gs[g] = (per > 1 && !group_max) ? m1 + m2 : m1;
     }
     __syncwarp();
     // the `keep` best groups, one after the other; a kept group is marked by +inf ... then turned into a flag
@@ -106,8 +120,13 @@ moe_route_kernel(const float* __restrict__ logits, int64_t stride, const float* 
     total += s[bi];
     __syncwarp();
   }
-  if (renorm) {
-    for (int r = lane; r < top; r += 32) weights[(int64_t)i * top + r] /= total;
+  if (renorm || weight_scale != 1.0f) {
+    __syncwarp();
+    for (int r = lane; r < top; r += 32) {
+      float wv = weights[(int64_t)i * top + r];
+      if (renorm) wv /= total + renorm_eps;
+      weights[(int64_t)i * top + r] = wv * weight_scale;
+    }
   }
 }
 
@@ -174,7 +193,8 @@ template <typename T>
 __global__ void __launch_bounds__(MG_THREADS)
 moe_gemm_kernel(const T* __restrict__ a, int64_t a_stride, int a_div, const T* __restrict__ w, int64_t w_expert_stride,
                 int64_t up_offset, const int* __restrict__ sorted, const int* __restrict__ tile_expert,
-                const int* __restrict__ num_tiles, T* __restrict__ out_t, float* __restrict__ out_f, int n_cols, int k) {
+                const int* __restrict__ num_tiles, T* __restrict__ out_t, float* __restrict__ out_f, int n_cols, int k,
+                int act) {
   __shared__ float As[MG_M][MG_K + 1];
   __shared__ float Bs[MG_N][MG_K + 1];
   __shared__ float Us[MG_N][MG_K + 1];
@@ -233,6 +253,9 @@ moe_gemm_kernel(const T* __restrict__ a, int64_t a_stride, int a_div, const T* _
       if (gated) {
         const float g = acc[i][j];
         out_t[(int64_t)p * n_cols + c] = from_float<T>(g / (1.0f + expf(-g)) * acu[i][j]);
+      } else if (act == 1) {
+        const float r = fmaxf(acc[i][j], 0.f);
+        out_t[(int64_t)p * n_cols + c] = from_float<T>(r * r);
       } else {
         out_f[(int64_t)p * n_cols + c] = acc[i][j];
       }
@@ -243,38 +266,51 @@ moe_gemm_kernel(const T* __restrict__ a, int64_t a_stride, int a_div, const T* _
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const T* __restrict__ shared,
-                   T* __restrict__ out, const int* __restrict__ row_of_pair, int top, int width) {
+                   T* __restrict__ out, const int* __restrict__ row_of_pair, int top, int width,
+                   const float* __restrict__ shared_gate, int64_t shared_gate_stride) {
   pdl_trigger();
   pdl_wait();
   const int64_t t = blockIdx.x;
+  const float sg = (shared && shared_gate) ? 1.0f / (1.0f + expf(-shared_gate[t * shared_gate_stride])) : 1.0f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < top; ++s) {
       const int64_t row = row_of_pair ? (int64_t)row_of_pair[t * top + s] : t * top + s;
       acc = fmaf(weights[t * top + s], y[row * width + c], acc);
     }
-    if (shared) acc += to_float(shared[t * width + c]);
+    if (shared) acc = fmaf(sg, to_float(shared[t * width + c]), acc);
     out[t * width + c] = from_float<T>(acc);
+  }
+}
+
+// out = max(in, 0)^2 rounded to T: the activation of experts without a gate, between the two tensor-core products.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_relu_sq_kernel(const float* __restrict__ in, T* __restrict__ out, int64_t n) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float r = fmaxf(in[i], 0.f);
+    out[i] = from_float<T>(r * r);
   }
 }
 
 template <typename T>
 int moe_gemm_launch(const T* a, int64_t a_stride, int a_div, const T* w, int64_t w_expert_stride, int64_t up_offset,
                     const int* sorted, const int* tile_expert, const int* num_tiles, void* out, int max_tiles,
-                    int n_cols, int k, int tile_m, cudaStream_t stream) {
+                    int n_cols, int k, int tile_m, int act, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
-  if (tile_m != MG_M || n_cols < 1 || k < 1 || a_div < 1) return (int)cudaErrorInvalidValue;
-  const bool gated = up_offset != 0;
+  if (tile_m != MG_M || n_cols < 1 || k < 1 || a_div < 1 || act < 0 || act > 1) return (int)cudaErrorInvalidValue;
+  const bool gated = up_offset != 0 || act == 1;
   return gllm_launch(moe_gemm_kernel<T>, dim3(max_tiles, (n_cols + MG_N - 1) / MG_N), dim3(MG_THREADS), 0, stream, a,
                      a_stride, a_div, w, w_expert_stride, up_offset, sorted, tile_expert, num_tiles,
-                     gated ? (T*)out : (T*)nullptr, gated ? (float*)nullptr : (float*)out, n_cols, k);
+                     gated ? (T*)out : (T*)nullptr, gated ? (float*)nullptr : (float*)out, n_cols, k, act);
 }
 }  // namespace
 
 GLLM_API int gllm_moe_route(const float* logits, int64_t stride, const float* correction, int* ids, float* weights,
-                            int n_tokens, int experts, int top, int groups, int keep, int renorm, int reserved,
-                            cudaStream_t stream) {
-  (void)reserved;
+                            int n_tokens, int experts, int top, int groups, int keep, int renorm, int softmax_scores,
+                            int group_max, float renorm_eps, float weight_scale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (experts < 1 || top < 1 || top > experts || groups < 1 || experts % groups || keep < 1 || keep > groups ||
       top > keep * (experts / groups))
@@ -282,7 +318,7 @@ GLLM_API int gllm_moe_route(const float* logits, int64_t stride, const float* co
   const size_t smem = sizeof(float) * (size_t)(2 * experts + groups);
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   return gllm_launch(moe_route_kernel, dim3(n_tokens), dim3(32), smem, stream, logits, stride, correction, ids, weights,
-                     experts, top, groups, keep, renorm);
+                     experts, top, groups, keep, renorm, softmax_scores, group_max, renorm_eps, weight_scale);
 }
 
 GLLM_API int gllm_moe_align(const int* ids, int* sorted, int* tile_expert, int* num_tiles, int* row_of_pair,
@@ -296,30 +332,31 @@ GLLM_API int gllm_moe_align(const int* ids, int* sorted, int* tile_expert, int* 
 
 GLLM_API int gllm_moe_gemm_f32(const float* a, int64_t a_stride, int a_div, const float* w, int64_t w_expert_stride,
                                int64_t up_offset, const int* sorted, const int* tile_expert, const int* num_tiles,
-                               void* out, int max_tiles, int n_cols, int k, int tile_m, cudaStream_t stream) {
+                               void* out, int max_tiles, int n_cols, int k, int tile_m, int act, cudaStream_t stream) {
   return moe_gemm_launch<float>(a, a_stride, a_div, w, w_expert_stride, up_offset, sorted, tile_expert, num_tiles, out,
-                                max_tiles, n_cols, k, tile_m, stream);
+                                max_tiles, n_cols, k, tile_m, act, stream);
 }
 GLLM_API int gllm_moe_gemm_bf16(const __nv_bfloat16* a, int64_t a_stride, int a_div, const __nv_bfloat16* w,
                                 int64_t w_expert_stride, int64_t up_offset, const int* sorted, const int* tile_expert,
                                 const int* num_tiles, void* out, int max_tiles, int n_cols, int k, int tile_m,
-                                cudaStream_t stream) {
+                                int act, cudaStream_t stream) {
   return moe_gemm_launch<__nv_bfloat16>(a, a_stride, a_div, w, w_expert_stride, up_offset, sorted, tile_expert,
-                                        num_tiles, out, max_tiles, n_cols, k, tile_m, stream);
+                                        num_tiles, out, max_tiles, n_cols, k, tile_m, act, stream);
 }
 
 GLLM_API int gllm_moe_combine_f32(const float* y, const float* weights, const float* shared, float* out,
-                                  const int* row_of_pair, int n_tokens, int top, int width, cudaStream_t stream) {
+                                  const int* row_of_pair, int n_tokens, int top, int width, const float* shared_gate,
+                                  int64_t shared_gate_stride, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   return gllm_launch(moe_combine_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, y, weights, shared, out,
-                     row_of_pair, top, width);
+                     row_of_pair, top, width, shared_gate, shared_gate_stride);
 }
 GLLM_API int gllm_moe_combine_bf16(const float* y, const float* weights, const __nv_bfloat16* shared,
                                    __nv_bfloat16* out, const int* row_of_pair, int n_tokens, int top, int width,
-                                   cudaStream_t stream) {
+                                   const float* shared_gate, int64_t shared_gate_stride, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   return gllm_launch(moe_combine_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, y, weights, shared, out,
-                     row_of_pair, top, width);
+                     row_of_pair, top, width, shared_gate, shared_gate_stride);
 }
 GLLM_API int gllm_moe_gather_bf16(const __nv_bfloat16* x, int64_t x_stride, const int* row_of_pair, __nv_bfloat16* out,
                                   int n_pairs, int top, int width, cudaStream_t stream) {
@@ -327,4 +364,11 @@ GLLM_API int gllm_moe_gather_bf16(const __nv_bfloat16* x, int64_t x_stride, cons
   if (width % 8 || x_stride % 8 || top < 1 || (reinterpret_cast<uintptr_t>(x) & 15)) return (int)cudaErrorInvalidValue;
   return gllm_launch(moe_gather_kernel<__nv_bfloat16>, dim3(n_pairs), dim3(256), 0, stream, x, x_stride, row_of_pair, out,
                      top, width);
+}
+
+GLLM_API int gllm_moe_relu_sq_bf16(const float* in, __nv_bfloat16* out, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > (int64_t)gllm_sm_count() * 8) blocks = (int64_t)gllm_sm_count() * 8;
+  return gllm_launch(moe_relu_sq_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, in, out, n);
 }

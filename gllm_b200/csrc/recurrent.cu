@@ -301,7 +301,10 @@ exp_gate_scan_kernel(const float* __restrict__ gates, int64_t gates_stride, cons
 // exponential gates): i = cap * tanh((i_raw + i_bias) / cap), f = logsigmoid(cap * tanh((f_raw + f_bias) / cap)),
 // m' = max(f + m, i), a = exp(f + m - m'), b[d] = exp(i - m') * k[d], q = q_raw * q_scale; the state
 // has one column more than there are value columns, fed with ones, which carries the normaliser n, and
-// the output gets two columns more: n . q and exp(-m').
+// the output gets two columns more: n . q and exp(-m').  mode 2 (state-space duality): one step size per (token, head),
+// dt = softplus(dt_raw + dt_bias[h]); a = exp(A[h] * dt) for the whole head (A = -exp(A_log) arrives in `lower`),
+// b[d] = dt * k[d] (k: the input projection B), q: the read-out projection C; heads share B and C in groups of
+// `kv_div` neighbouring heads.
 // A block owns `cols` columns of one (request, head); `lanes` threads share a column, each keeping DPT of its
 // key channels (4 for up to 128 key channels, 16 beyond; 8 for 65..128 measured the same: the recurrence is a chain from token to token, bounded
 // by the instructions a warp spends per token, so the state is spread over many threads).  Tokens are taken in chunks of `tc`: while a chunk is computed from shared memory, the raw
@@ -327,7 +330,7 @@ matrix_recurrence_kernel(int,
                          float* __restrict__ state,                       // [slots, heads, dvx, dk]
                          const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                          float* __restrict__ out, int64_t out_stride,     // [n, heads * out_cols]
-                         int heads, int dk, int dv, int lanes, int tc) {
+                         int heads, int dk, int dv, int lanes, int tc, int kv_div) {
   constexpr int PF = REC_LOOKAHEAD / THREADS;
   constexpr int mode = MODE;
   extern __shared__ __align__(16) float smem[];
@@ -364,6 +367,7 @@ matrix_recurrence_kernel(int,
   const int d_mine = threadIdx.x & (dkp - 1), tt_q0 = threadIdx.x / dkp, tt_qstep = fast ? THREADS / dkp : 0;
   const int c_mine = threadIdx.x & (cols - 1), tt_v0 = threadIdx.x / cols, tt_vstep = lanes;   // THREADS / cols
   const int hd_mine = h * dk + min(d_mine, dk - 1);
+  const int kd_mine = (h / kv_div) * dk + min(d_mine, dk - 1);      // q and k: shared by kv_div heads
   const int cg_mine = blockIdx.x * cols + c_mine;
   const float lo_mine = (mode == 0 && fast && d_mine < dk) ? lower[hd_mine] : 0.f;
   const float gb_mine = (mode == 0 && fast && d_mine < dk) ? gate_bias[hd_mine] : 0.f;
@@ -376,8 +380,8 @@ matrix_recurrence_kernel(int,
         pq[j] = pg[j] = 0u;
         if (d_mine < dk) {
           const int64_t t = t0 + tt;
-          pq[j] = load_ahead(q + t * q_stride + hd_mine);
-          pg[j] = mode == 1 ? load_ahead(k + t * k_stride + hd_mine) : load_ahead(gates + t * gates_stride + hd_mine);
+          pq[j] = load_ahead(q + t * q_stride + kd_mine);
+          pg[j] = mode >= 1 ? load_ahead(k + t * k_stride + kd_mine) : load_ahead(gates + t * gates_stride + hd_mine);
         }
       }
     } else {
@@ -389,9 +393,9 @@ matrix_recurrence_kernel(int,
         pq[j] = pg[j] = 0u;
         if (d < dk) {
           const int64_t t = t0 + tt;
-          const int hd = h * dk + d;
-          pq[j] = load_ahead(q + t * q_stride + hd);
-          pg[j] = mode == 1 ? load_ahead(k + t * k_stride + hd) : load_ahead(gates + t * gates_stride + hd);
+          const int hd = h * dk + d, kd = (h / kv_div) * dk + d;
+          pq[j] = load_ahead(q + t * q_stride + kd);
+          pg[j] = mode >= 1 ? load_ahead(k + t * k_stride + kd) : load_ahead(gates + t * gates_stride + hd);
         }
       }
     }
@@ -408,6 +412,7 @@ matrix_recurrence_kernel(int,
       pmp = load_ahead(g + 2 * heads + h);
       pmn = load_ahead(g + 3 * heads + h);
     }
+    if (mode == 2 && (int)threadIdx.x < nt) pi = load_ahead(gates + (int64_t)(t0 + threadIdx.x) * gates_stride + h);
   };
   auto stash = [&](int nt, float* buf) {
     float* q_s = buf;
@@ -420,7 +425,7 @@ matrix_recurrence_kernel(int,
         const int tt = tt_q0 + j * tt_qstep;
         if (tt >= nt) break;
         const int idx = tt * dkp + d_mine;
-        if (mode == 1) {
+        if (mode >= 1) {
           q_s[idx] = as_value<T>(pq[j]) * q_scale;
           g_s[idx] = as_value<T>(pg[j]);
         } else {
@@ -434,7 +439,7 @@ matrix_recurrence_kernel(int,
         const int idx = threadIdx.x + j * THREADS;
         if (idx >= nt * dkp) break;
         const int d = idx % dkp;
-        if (mode == 1) {
+        if (mode >= 1) {
           q_s[idx] = as_value<T>(pq[j]) * q_scale;
           g_s[idx] = as_value<T>(pg[j]);
         } else {
@@ -456,6 +461,11 @@ matrix_recurrence_kernel(int,
       sc_s[threadIdx.x] = expf(as_value<float>(pf) + as_value<float>(pmp) - m_new);          // keep
       sc_s[tc + threadIdx.x] = expf(as_value<float>(pi) - m_new);                            // take
       sc_s[2 * tc + threadIdx.x] = expf(-m_new);
+    }
+    if (mode == 2 && (int)threadIdx.x < nt) {
+      const float dt = softplusf_(as_value<float>(pi) + gate_bias[h]);
+      sc_s[threadIdx.x] = expf(lower[h] * dt);                                               // keep
+      sc_s[tc + threadIdx.x] = dt;                                                           // take
     }
   };
 
@@ -480,7 +490,7 @@ matrix_recurrence_kernel(int,
     for (int tt = 0; tt < nt; ++tt) {
       const float vj = v_s[tt * cols + cix];
       float keep = 0.f, take = 0.f;
-      if (mode == 1) {
+      if (mode >= 1) {
         keep = sc_s[tt];
         take = sc_s[tc + tt];
       }
@@ -494,8 +504,8 @@ matrix_recurrence_kernel(int,
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = i4 * 4 + e;
-          const float a = mode == 1 ? keep : ga[e];
-          const float b = mode == 1 ? take * ga[e] : 1.0f - ga[e];
+          const float a = mode >= 1 ? keep : ga[e];
+          const float b = mode >= 1 ? take * ga[e] : 1.0f - ga[e];
           S[i] = a * S[i] + b * vj;
           o = fmaf(S[i], qa[e], o);
         }
@@ -601,7 +611,7 @@ matrix_recurrence_step_kernel(int mode, const T* __restrict__ q, int64_t q_strid
                               const float* __restrict__ lower, float q_scale, float* __restrict__ state,
                               const int* __restrict__ cu_q,
                               const int* __restrict__ state_slots, float* __restrict__ out, int64_t out_stride, int heads,
-                              int dk, int dv, int lanes) {
+                              int dk, int dv, int lanes, int kv_div) {
   pdl_trigger();
   pdl_wait();
   const int cols = REC_THREADS / lanes;
@@ -620,6 +630,9 @@ matrix_recurrence_step_kernel(int mode, const T* __restrict__ q, int64_t q_strid
     m_new = g[3 * heads + h];
     keep = expf(g[heads + h] + g[2 * heads + h] - m_new);
     take = expf(g[h] - m_new);
+  } else if (mode == 2) {
+    take = softplusf_(gates[t * gates_stride + h] + gate_bias[h]);          // the step size
+    keep = expf(lower[h] * take);
   }
   const float vj = !live ? 0.f : (col < dv ? to_float(v[t * v_stride + (int64_t)h * dv + col]) : 1.0f);
   float* sp = state + (((int64_t)slot * heads + h) * dvx + (live ? col : 0)) * dk;
@@ -638,12 +651,12 @@ matrix_recurrence_step_kernel(int mode, const T* __restrict__ q, int64_t q_strid
     for (int e = 0; e < 4; ++e) {
       const int d = d0 + e;
       if (d < dk) {
-        const int hd = h * dk + d;
+        const int hd = h * dk + d, kd = (h / kv_div) * dk + d;
         float a, b, qe;
-        if (mode == 1) {
+        if (mode >= 1) {
           a = keep;
-          b = take * to_float(k[t * k_stride + hd]);
-          qe = to_float(q[t * q_stride + hd]) * q_scale;
+          b = take * to_float(k[t * k_stride + kd]);
+          qe = to_float(q[t * q_stride + kd]) * q_scale;
         } else {
           const float lo = lower[hd];
           a = lo + (1.0f - lo) * sigmoidf_(gates[t * gates_stride + hd] + gate_bias[hd]);
@@ -699,6 +712,58 @@ head_norm_kernel(const float* __restrict__ o, int64_t o_stride, int o_cols, int 
     float x = (with_den ? row[c] * inv_den : row[c]) * inv * w[(int64_t)h * w_head_stride + c];
     if (gate) x *= sigmoidf_(to_float(gate[(int64_t)t * gate_stride + (int64_t)h * dv + c]));
     out[(int64_t)t * out_stride + (int64_t)h * dv + c] = from_float<T>(x);
+  }
+}
+
+// --------------------------------------------------------------- gated norm over groups of columns
+// One block per (token, group of `group_width` neighbouring columns):
+//     u[c] = (y[c] + skip[c / head_width] * x[c]) * silu(z[c])        (the skip term only with `skip`)
+//     out[c] = u[c] / sqrt(mean over the group of u^2 + eps) * w[c]
+// y is the fp32 read-out of a recurrence, x its input and z the gate, both of the activation type.  The gate comes
+// BEFORE the norm, and the groups need not be heads.  Two passes over the group's columns; everything in fp32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ y, int64_t y_stride, const T* __restrict__ x, int64_t x_stride,
+                        const float* __restrict__ skip, int head_width, const T* __restrict__ z, int64_t z_stride,
+                        const float* __restrict__ w, T* __restrict__ out, int64_t out_stride, int group_width,
+                        float eps) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  const int c0 = blockIdx.y * group_width;
+  auto gated = [&](int c) {
+    float u = y[t * y_stride + c];
+    if (skip) u = fmaf(skip[c / head_width], to_float(x[t * x_stride + c]), u);
+    return u * siluf_(to_float(z[t * z_stride + c]));
+  };
+  float ss = 0.f;
+  for (int c = c0 + threadIdx.x; c < c0 + group_width; c += blockDim.x) {
+    const float u = gated(c);
+    ss = fmaf(u, u, ss);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)group_width + eps);
+  for (int c = c0 + threadIdx.x; c < c0 + group_width; c += blockDim.x)
+    out[t * out_stride + c] = from_float<T>(gated(c) * inv * w[c]);
+}
+
+// The convolution's state after a step: of (old state ++ this step's inputs) the last taps-1 rows, per request.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_state_advance_kernel(const T* __restrict__ x, int64_t x_stride, float* __restrict__ conv_state,
+                          const int* __restrict__ cu_q, const int* __restrict__ state_slots, int channels, int taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int t0 = cu_q[r], len = cu_q[r + 1] - t0;
+  const int keep = taps - 1;
+  float* cs = conv_state + (int64_t)state_slots[r] * keep * channels + c;
+  for (int j = 0; j < keep; ++j) {           // ascending: a row is read before the row that overwrites it is written
+    const int src = j + len;                 // row of (old state ++ inputs)
+    cs[(int64_t)j * channels] =
+        src < keep ? cs[(int64_t)src * channels] : to_float(x[(int64_t)(t0 + src - keep) * x_stride + c]);
   }
 }
 
@@ -762,9 +827,12 @@ int matrix_recurrence_launch(int mode, const T* q, int64_t q_stride, const T* k,
                              int64_t v_stride, const float* gates, int64_t gates_stride, const float* gate_bias,
                              const float* lower, float cap, float q_scale, float* state, float* mstate, float* work,
                              const int* cu_q, const int* state_slots, float* out, int64_t out_stride,
-                             int num_requests, int max_q_len, int heads, int dk, int dv, cudaStream_t stream) {
+                             int num_requests, int max_q_len, int heads, int dk, int dv, int kv_div,
+                             cudaStream_t stream) {
   if (num_requests <= 0) return 0;
-  if (heads > 65535 || num_requests > 65535 || dk < 1 || dv < 1 || dk > 512) return (int)cudaErrorInvalidValue;
+  if (heads > 65535 || num_requests > 65535 || dk < 1 || dv < 1 || dk > 512 || mode < 0 || mode > 2 || kv_div < 1 ||
+      heads % kv_div || (mode == 2 && (k == nullptr || lower == nullptr)))
+    return (int)cudaErrorInvalidValue;
   const int dvx = dv + (mode == 1 ? 1 : 0);
   if (mode == 1) {
     if (work == nullptr || mstate == nullptr) return (int)cudaErrorInvalidValue;
@@ -780,7 +848,7 @@ int matrix_recurrence_launch(int mode, const T* q, int64_t q_stride, const T* k,
     const int cols = REC_THREADS / lanes;
     return gllm_launch(matrix_recurrence_step_kernel<T>, dim3((dvx + cols - 1) / cols, heads, num_requests),
                        dim3(REC_THREADS), 0, stream, mode, q, q_stride, k, k_stride, v, v_stride, gates, gates_stride,
-                       gate_bias, lower, q_scale, state, cu_q, state_slots, out, out_stride, heads, dk, dv, lanes);
+                       gate_bias, lower, q_scale, state, cu_q, state_slots, out, out_stride, heads, dk, dv, lanes, kv_div);
   }
   const int dpt = dk <= 128 ? 4 : 16;
   int lanes = pow2_at_least((dk + dpt - 1) / dpt);
@@ -793,8 +861,9 @@ int matrix_recurrence_launch(int mode, const T* q, int64_t q_stride, const T* k,
   if (tc * dkp > REC_LOOKAHEAD || tc * cols > REC_LOOKAHEAD) return (int)cudaErrorInvalidValue;
   const size_t smem = sizeof(float) * 2 * (size_t)tc * (2 * dkp + cols + 4);
   void (*kernel)(int, const T*, int64_t, const T*, int64_t, const T*, int64_t, const float*, int64_t, const float*,
-                 const float*, float, float*, const int*, const int*, float*, int64_t, int, int, int, int, int);
-  if (mode == 1) kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4, REC_THREADS, 1> : matrix_recurrence_kernel<T, 16, REC_THREADS, 1>;
+                 const float*, float, float*, const int*, const int*, float*, int64_t, int, int, int, int, int, int);
+  if (mode == 2) kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4, REC_THREADS, 2> : matrix_recurrence_kernel<T, 16, REC_THREADS, 2>;
+  else if (mode == 1) kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4, REC_THREADS, 1> : matrix_recurrence_kernel<T, 16, REC_THREADS, 1>;
   else kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4, REC_THREADS, 0> : matrix_recurrence_kernel<T, 16, REC_THREADS, 0>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -802,7 +871,7 @@ int matrix_recurrence_launch(int mode, const T* q, int64_t q_stride, const T* k,
   }
   return gllm_launch(kernel, dim3((dvx + cols - 1) / cols, heads, num_requests), dim3(threads), smem, stream, mode, q,
                      q_stride, k, k_stride, v, v_stride, gates, gates_stride, gate_bias, lower, q_scale, state, cu_q,
-                     state_slots, out, out_stride, heads, dk, dv, lanes, tc);
+                     state_slots, out, out_stride, heads, dk, dv, lanes, tc, kv_div);
 }
 
 template <typename T>
@@ -814,6 +883,27 @@ int head_norm_launch(const float* o, int64_t o_stride, int o_cols, int with_den,
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
   return gllm_launch(head_norm_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, o, o_stride, o_cols, with_den,
                      den_eps, w, w_head_stride, gate, gate_stride, out, out_stride, n_tokens, heads, dv, eps);
+}
+
+template <typename T>
+int gated_group_norm_launch(const float* y, int64_t y_stride, const T* x, int64_t x_stride, const float* skip,
+                            int head_width, const T* z, int64_t z_stride, const float* w, T* out, int64_t out_stride,
+                            int n_tokens, int groups, int group_width, float eps, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (groups < 1 || groups > 65535 || group_width < 1 || (skip != nullptr && (x == nullptr || head_width < 1)))
+    return (int)cudaErrorInvalidValue;
+  const int threads = group_width >= 256 ? 256 : (group_width + 31) / 32 * 32;
+  return gllm_launch(gated_group_norm_kernel<T>, dim3(n_tokens, groups), dim3(threads), 0, stream, y, y_stride, x,
+                     x_stride, skip, head_width, z, z_stride, w, out, out_stride, group_width, eps);
+}
+
+template <typename T>
+int conv_state_advance_launch(const T* x, int64_t x_stride, float* conv_state, const int* cu_q, const int* state_slots,
+                              int num_requests, int channels, int taps, cudaStream_t stream) {
+  if (num_requests <= 0 || taps <= 1) return 0;
+  if (num_requests > 65535 || taps > MAX_TAPS) return (int)cudaErrorInvalidValue;
+  return gllm_launch(conv_state_advance_kernel<T>, dim3((channels + 255) / 256, num_requests), dim3(256), 0, stream, x,
+                     x_stride, conv_state, cu_q, state_slots, channels, taps);
 }
 }  // namespace
 
@@ -838,10 +928,11 @@ int head_norm_launch(const float* o, int64_t o_stride, int o_cols, int with_den,
                                           const float* gate_bias, const float* lower, float cap, float q_scale,       \
                                           float* state, float* mstate, float* work, const int* cu_q,                  \
                                           const int* state_slots, float* out, int64_t out_stride, int num_requests,   \
-                                          int max_q_len, int heads, int dk, int dv, cudaStream_t stream) {            \
+                                          int max_q_len, int heads, int dk, int dv, int kv_div,                       \
+                                          cudaStream_t stream) {                                                      \
     return matrix_recurrence_launch<T>(mode, q, q_stride, k, k_stride, v, v_stride, gates, gates_stride, gate_bias,   \
                                        lower, cap, q_scale, state, mstate, work, cu_q, state_slots, out, out_stride,  \
-                                       num_requests, max_q_len, heads, dk, dv, stream);                               \
+                                       num_requests, max_q_len, heads, dk, dv, kv_div, stream);                       \
   }                                                                                                                   \
   GLLM_API int gllm_head_norm_##S(const float* o, int64_t o_stride, int o_cols, int with_den, float den_eps,          \
                                   const float* w, int w_head_stride, const T* gate, int64_t gate_stride, T* out,      \
@@ -849,6 +940,19 @@ int head_norm_launch(const float* o, int64_t o_stride, int o_cols, int with_den,
                                   cudaStream_t stream) {                                                              \
     return head_norm_launch<T>(o, o_stride, o_cols, with_den, den_eps, w, w_head_stride, gate, gate_stride, out,      \
                                out_stride, n_tokens, heads, dv, eps, stream);                                         \
+  }                                                                                                                   \
+  GLLM_API int gllm_gated_group_norm_##S(const float* y, int64_t y_stride, const T* x, int64_t x_stride,              \
+                                         const float* skip, int head_width, const T* z, int64_t z_stride,             \
+                                         const float* w, T* out, int64_t out_stride, int n_tokens, int groups,        \
+                                         int group_width, float eps, cudaStream_t stream) {                           \
+    return gated_group_norm_launch<T>(y, y_stride, x, x_stride, skip, head_width, z, z_stride, w, out, out_stride,    \
+                                      n_tokens, groups, group_width, eps, stream);                                    \
+  }                                                                                                                   \
+  GLLM_API int gllm_conv_state_advance_##S(const T* x, int64_t x_stride, float* conv_state, const int* cu_q,          \
+                                           const int* state_slots, int num_requests, int channels, int taps,          \
+                                           cudaStream_t stream) {                                                     \
+    return conv_state_advance_launch<T>(x, x_stride, conv_state, cu_q, state_slots, num_requests, channels, taps,     \
+                                        stream);                                                                      \
   }
 
 GLLM_RECURRENT_EXPORTS(float, f32)

@@ -49,6 +49,7 @@ __all__ = [
     "qk_rownorm",
     "Pending",
     "rope_norm_store",
+    "add_dyt",
 ]
 
 P = c_void_p
@@ -83,7 +84,10 @@ _SIGNATURES = {
         "gllm_selective_scan_{t}": [P, P, P, P, P, c_int64, c_int, c_int, P, P, c_int64, c_int, P, P, P, P, P, c_int,
                                     c_int, c_int, c_int, c_int, P],
         "gllm_matrix_recurrence_{t}": [c_int, P, c_int64, P, c_int64, P, c_int64, P, c_int64, P, P, c_float, c_float,
-                                       P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int, P],
+                                       P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, P],
+        "gllm_gated_group_norm_{t}": [P, c_int64, P, c_int64, P, c_int, P, c_int64, P, P, c_int64, c_int, c_int, c_int,
+                                      c_float, P],
+        "gllm_conv_state_advance_{t}": [P, c_int64, P, P, P, c_int, c_int, c_int, P],
         "gllm_head_norm_{t}": [P, c_int64, c_int, c_int, c_float, P, c_int, P, c_int64, P, c_int64, c_int, c_int,
                                c_int, c_float, P],
     },
@@ -104,6 +108,15 @@ _SIGNATURES = {
         "gllm_attention_latent_{t}": [P, c_int64, c_int, P, c_int64, c_int, P, c_int64, P, c_int64, c_int, P, P, c_int,
                                       P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P],
     },
+    "dyt_norm": {
+        "gllm_add_dyt_{t}": [P, P, c_int, c_int64, P, P, P, P, P, P, c_int, c_int, P],
+    },
+    "attention_diff": {
+        "gllm_diff_rope_store_{t}": [P, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, P, P],
+        "gllm_attention_diff_{t}": [P, c_int64, P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, c_int, c_int, c_int,
+                                    c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float, P, P],
+    },
     "postnorm": {
         "gllm_postnorm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, c_float, P, P, P, c_float, P, P, c_int, c_int, P],
     },
@@ -117,10 +130,12 @@ _SIGNATURES = {
         "gllm_delta_rule": [P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
     },
     "moe": {
-        "gllm_moe_route": [P, c_int64, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
+        "gllm_moe_route": [P, c_int64, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                           P],
         "gllm_moe_align": [P, P, P, P, P, c_int, c_int, c_int, c_int, P],
-        "gllm_moe_gemm_{t}": [P, c_int64, c_int, P, c_int64, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, P],
-        "gllm_moe_combine_{t}": [P, P, P, P, P, c_int, c_int, c_int, P],
+        "gllm_moe_gemm_{t}": [P, c_int64, c_int, P, c_int64, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
+        "gllm_moe_combine_{t}": [P, P, P, P, P, c_int, c_int, c_int, P, c_int64, P],
+        "gllm_moe_relu_sq_bf16": [P, P, c_int64, P],
         "gllm_moe_gather_{t}": [P, c_int64, P, P, c_int, c_int, c_int, P],
     },
     "attention_simt": {
@@ -522,6 +537,45 @@ def _pending_add_rmsnorm(pending: Pending, resid, weight, eps, out_dtype, rows, 
     _check(f(_ptr(value), parts_ptr, n_parts, part_stride, _ptr(pending.post_weight), pending.post_eps,
              _ptr(pending.extra), resid.data_ptr(), weight.data_ptr(), float(eps), out.data_ptr(), _ptr(rows), n_rows,
              hidden, _stream()), "postnorm_add_rmsnorm")
+    return out
+
+
+# ------------------------------------------------------- add + a norm without a statistic
+def add_dyt(branch, resid: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+            out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``resid += branch`` (fp32, in place) then ``tanh(alpha * resid) * weight + bias``: a norm that takes no
+    statistic of its row.  ``alpha``: one fp32 number on the device.  ``branch``: a tensor of ``out_dtype``, a
+    SplitSum, a plain ``Pending`` or None.  With ``rows`` only those rows are computed and ``resid`` is left untouched."""
+    _cuda(resid, "resid", torch.float32)
+    _cuda(alpha, "alpha", torch.float32)
+    _cuda(weight, "weight", torch.float32)
+    hidden = resid.shape[-1]
+    if weight.numel() != hidden or alpha.numel() != 1 or (bias is not None and bias.numel() != hidden):
+        raise ValueError("the norm takes one alpha and one weight (and bias) value per column")
+    if bias is not None:
+        _cuda(bias, "bias", torch.float32)
+    if isinstance(branch, Pending):
+        if branch.post_weight is not None or branch.extra is not None:
+            raise ValueError("this norm takes a plain pending branch only")
+        branch = branch.value
+    parts_ptr, n_parts, part_stride = _parts_args(branch)
+    if isinstance(branch, SplitSum):
+        if tuple(branch.shape) != tuple(resid.shape) or branch.dtype != out_dtype:
+            raise ValueError("branch and resid differ in shape or dtype")
+        branch = None
+    elif branch is not None:
+        _cuda(branch, "branch", out_dtype)
+        if branch.shape != resid.shape:
+            raise ValueError("branch and resid differ in shape")
+    if rows is not None:
+        _cuda(rows, "rows", torch.int32)
+        n_rows = rows.numel()
+    else:
+        n_rows = resid.numel() // hidden
+    out = torch.empty((n_rows, hidden), dtype=out_dtype, device=resid.device)
+    f = _fn("dyt_norm", f"gllm_add_dyt_{_suffix(out_dtype)}")
+    _check(f(_ptr(branch), parts_ptr, n_parts, part_stride, resid.data_ptr(), alpha.data_ptr(), weight.data_ptr(),
+             _ptr(bias), out.data_ptr(), _ptr(rows), n_rows, hidden, _stream()), "add_dyt")
     return out
 
 

@@ -58,6 +58,8 @@ MODULES = {
     "rope_norm": "rope_norm.cu",
     "delta_rule": "delta_rule.cu",
     "moe": "moe.cu",
+    "dyt_norm": "dyt_norm.cu",
+    "attention_diff": "attention_diff.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

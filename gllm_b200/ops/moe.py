@@ -13,11 +13,15 @@ TENSOR_CORE_TILE_ROWS = 128     # the same for the tcgen05 products (the rows of
 
 
 def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int = 1, groups_kept: int = 1,
-          renormalize: bool = False):
+          renormalize: bool = False, score: str = "sigmoid", group_score: str = "top2", renormalize_eps: float = 0.0,
+          scale: float = 1.0):
     """From fp32 router logits ``[n, experts]`` to the chosen experts ``[n, top]`` int32 and their weights fp32.
-    Scores ``s = sigmoid(logits)``; the choice is made on ``s + correction`` among the experts of the
-    ``groups_kept`` best of ``groups`` equal groups of neighbours (a group's score: the sum of its two largest
-    choice scores); the weights are the chosen ``s``, divided by their sum with ``renormalize``."""
+    Scores ``s = sigmoid(logits)`` (``score`` "softmax": the softmax over all experts); the choice is made on
+    ``s + correction`` among the experts of the ``groups_kept`` best of ``groups`` equal groups of neighbours (a
+    group's score: the sum of its two largest choice scores, with ``group_score`` "max" its largest); the weights are
+    the chosen ``s``, divided by their sum (plus ``renormalize_eps``) with ``renormalize``, times ``scale``."""
+    if score not in ("sigmoid", "softmax") or group_score not in ("top2", "max"):
+        raise ValueError("router scores are 'sigmoid' or 'softmax', group scores 'top2' or 'max'")
     _cuda(logits, "logits", torch.float32, contiguous=False)
     if logits.dim() != 2 or logits.stride(1) != 1:
         raise ValueError("router logits must be [tokens, experts] with contiguous columns")
@@ -30,7 +34,8 @@ def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, group
     weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     _check(_fn("moe", "gllm_moe_route")(logits.data_ptr(), logits.stride(0), _ptr(correction), ids.data_ptr(),
                                         weights.data_ptr(), n, experts, int(top), int(groups), int(groups_kept),
-                                        int(renormalize), 0, _stream()), "moe_route")
+                                        int(renormalize), int(score == "softmax"), int(group_score == "max"),
+                                        float(renormalize_eps), float(scale), _stream()), "moe_route")
     return ids, weights
 
 
@@ -64,37 +69,40 @@ def gather_rows(x: torch.Tensor, top: int, row_of_pair: torch.Tensor, rows: int)
     return out
 
 
-def tensor_cores_take(dtype: torch.dtype, width: int, ff: int) -> bool:
-    """Whether the experts' products run on the tcgen05 kernel: bf16, rows that start on 16 bytes, and gate and up
-    rows stacked in blocks of 64."""
-    return dtype == torch.bfloat16 and width % 8 == 0 and ff % 64 == 0
+def tensor_cores_take(dtype: torch.dtype, width: int, ff: int, gated: bool = True) -> bool:
+    """Whether the experts' products run on the tcgen05 kernel: bf16, rows that start on 16 bytes, and (for gated
+    experts) gate and up rows stacked in blocks of 64."""
+    return dtype == torch.bfloat16 and width % 8 == 0 and ff % (64 if gated else 8) == 0
 
 
-def expert_product(a: torch.Tensor, rows_per_input: int, weight: torch.Tensor, plan, n_pairs: int, gated: bool):
+def expert_product(a: torch.Tensor, rows_per_input: int, weight: torch.Tensor, plan, n_pairs: int, gated: bool,
+                   relu_squared: bool = False):
     """``out[pair] = a[pair // rows_per_input] @ weight[expert of pair].T`` for the pairs of ``plan`` (what
     ``align`` returned).  ``weight [experts, rows, k]``; ``gated``: its rows are gate rows then up rows and the
-    result is ``silu(gate) * up`` in the activation type ``[n_pairs, rows / 2]``; otherwise fp32 ``[n_pairs, rows]``."""
+    result is ``silu(gate) * up`` in the activation type ``[n_pairs, rows / 2]``; ``relu_squared`` (experts without a
+    gate): ``max(result, 0) ** 2`` in the activation type ``[n_pairs, rows]``; otherwise fp32 ``[n_pairs, rows]``."""
     _cuda(a, "a", contiguous=False)
     _cuda(weight, "weight", a.dtype)
     if a.dim() != 2 or a.stride(1) != 1 or weight.dim() != 3 or weight.shape[2] != a.shape[1]:
         raise ValueError("the expert product takes rows of contiguous columns and weights [experts, rows, k]")
     sorted_pairs, tile_expert, num_tiles = plan
     rows, k = weight.shape[1], weight.shape[2]
-    if gated and rows % 2:
-        raise ValueError("gate and up rows come in equal numbers")
+    if gated and (rows % 2 or relu_squared):
+        raise ValueError("gate and up rows come in equal numbers, and the gate is the activation")
     n_cols = rows // 2 if gated else rows
-    out = torch.empty((n_pairs, n_cols), dtype=a.dtype if gated else torch.float32, device=a.device)
+    out = torch.empty((n_pairs, n_cols), dtype=a.dtype if gated or relu_squared else torch.float32, device=a.device)
     f = _fn("moe", f"gllm_moe_gemm_{_suffix(a.dtype)}")
     _check(f(a.data_ptr(), a.stride(0), int(rows_per_input), weight.data_ptr(), weight.stride(0),
              n_cols * k if gated else 0, sorted_pairs.data_ptr(), tile_expert.data_ptr(), num_tiles.data_ptr(),
-             out.data_ptr(), tile_expert.numel(), n_cols, k, TILE_ROWS, _stream()), "moe_gemm")
+             out.data_ptr(), tile_expert.numel(), n_cols, k, TILE_ROWS, int(relu_squared), _stream()), "moe_gemm")
     return out
 
 
 def combine(y: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None, out_dtype: torch.dtype,
-            row_of_pair: torch.Tensor | None = None) -> torch.Tensor:
+            row_of_pair: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None) -> torch.Tensor:
     """``out[t] = sum_s weights[t, s] * y[t * top + s] (+ shared[t])``, summed in slot order in fp32; with
-    ``row_of_pair`` the pair's result is row ``row_of_pair[t * top + s]`` of ``y``."""
+    ``row_of_pair`` the pair's result is row ``row_of_pair[t * top + s]`` of ``y``; with ``shared_gate`` (fp32, one
+    logit per token; may be a column of a wider matrix) the shared result is multiplied by its sigmoid."""
     _cuda(y, "y", torch.float32)
     _cuda(weights, "weights", torch.float32)
     n, top = weights.shape
@@ -107,31 +115,51 @@ def combine(y: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None,
         _cuda(shared, "shared", out_dtype)
         if tuple(shared.shape) != (n, width):
             raise ValueError("the shared expert's result does not fit")
+    gate_stride = 0
+    if shared_gate is not None:
+        _cuda(shared_gate, "shared_gate", torch.float32, contiguous=False)
+        if shared is None or shared_gate.dim() != 1 or shared_gate.numel() != n:
+            raise ValueError("the shared expert's gate is one logit per token")
+        gate_stride = shared_gate.stride(0)
     out = torch.empty((n, width), dtype=out_dtype, device=y.device)
     _check(_fn("moe", f"gllm_moe_combine_{_suffix(out_dtype)}")(y.data_ptr(), weights.data_ptr(), _ptr(shared),
                                                                out.data_ptr(), _ptr(row_of_pair), n, top, width,
-                                                               _stream()), "moe_combine")
+                                                               _ptr(shared_gate), gate_stride, _stream()), "moe_combine")
+    return out
+
+
+def relu_squared_rows(x: torch.Tensor) -> torch.Tensor:
+    """``max(x, 0) ** 2`` of fp32 ``x``, rounded to bf16: between the two tensor-core products of experts without
+    a gate."""
+    _cuda(x, "x", torch.float32)
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    _check(_fn("moe", "gllm_moe_relu_sq_bf16")(x.data_ptr(), out.data_ptr(), x.numel(), _stream()), "moe_relu_sq")
     return out
 
 
 def apply_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-                  w_down: torch.Tensor, shared: torch.Tensor | None, tensor_cores: bool) -> torch.Tensor:
+                  w_down: torch.Tensor, shared: torch.Tensor | None, tensor_cores: bool, gated: bool = True,
+                  shared_gate: torch.Tensor | None = None) -> torch.Tensor:
     """``out[t] = sum_s weights[t, s] * expert_{ids[t, s]}(x[t]) (+ shared[t])`` with ``expert_e(x) = w_down[e]
     (silu(gate) * up)``.  ``tensor_cores``: ``w_gate_up [experts, 2 * ff, width]`` is stacked per expert by
     ``interleave_gate_up``; the tokens' rows are copied into the order of the sorted pairs, both products read and
     write rows in that order on the tcgen05 kernel, and the weighted sum looks every pair's row up.  Otherwise
-    ``w_gate_up`` holds an expert's gate rows, then its up rows, and the CUDA-core kernel runs."""
+    ``w_gate_up`` holds an expert's gate rows, then its up rows, and the CUDA-core kernel runs.  ``gated`` False:
+    experts without a gate, ``expert_e(x) = w_down[e] relu(w_up[e] x)^2`` with ``w_gate_up [experts, ff, width]`` the
+    up weights.  ``shared_gate``: see ``combine``."""
     experts, (_, top), pairs = w_gate_up.shape[0], ids.shape, ids.numel()
     if not tensor_cores:
         plan = align(ids, experts)
-        hidden = expert_product(x, top, w_gate_up, plan, pairs, gated=True)
+        hidden = expert_product(x, top, w_gate_up, plan, pairs, gated=gated, relu_squared=not gated)
         y = expert_product(hidden, 1, w_down, plan, pairs, gated=False)
-        return combine(y, weights, shared, x.dtype)
+        return combine(y, weights, shared, x.dtype, shared_gate=shared_gate)
     from gllm_b200.ops import gemm_bf16
 
     _, tile_expert, num_tiles, row_of_pair = align(ids, experts, TENSOR_CORE_TILE_ROWS, want_rows=True)
     wide = pairs > 2048
     xs = gather_rows(x, top, row_of_pair, tile_expert.numel() * TENSOR_CORE_TILE_ROWS)
-    hidden = gemm_bf16.linear_grouped(xs, w_gate_up, tile_expert, num_tiles, gated=True, wide=wide)
+    hidden = gemm_bf16.linear_grouped(xs, w_gate_up, tile_expert, num_tiles, gated=gated, wide=wide)
+    if not gated:
+        hidden = relu_squared_rows(hidden)
     y = gemm_bf16.linear_grouped(hidden, w_down, tile_expert, num_tiles, gated=False, wide=wide)
-    return combine(y, weights, shared, x.dtype, row_of_pair)
+    return combine(y, weights, shared, x.dtype, row_of_pair, shared_gate=shared_gate)

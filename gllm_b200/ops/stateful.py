@@ -153,13 +153,14 @@ def selective_scan(xc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor
 # ------------------------------------------------------------------ matrix recurrences
 GATED_LINEAR = 0      # a = f, b = 1 - f, f = lower + (1 - lower) sigmoid(raw + bias); q = silu(raw q)
 EXP_GATED = 1         # exponential input gate, log-sigmoid forget gate, running maximum, normaliser
+STEP_SIZED = 2        # one step size per (token, head): a = exp(A dt), b = dt * k, dt = softplus(raw + bias)
 
 
 def matrix_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor, gates: torch.Tensor,
                       gate_bias: torch.Tensor, lower: torch.Tensor | None, cap: float, q_scale: float,
                       state: torch.Tensor, mstate: torch.Tensor | None, cu_q: torch.Tensor,
                       state_slots: torch.Tensor, num_requests: int, heads: int, dk: int, dv: int,
-                      max_q_len: int = 0) -> torch.Tensor:
+                      max_q_len: int = 0, heads_per_group: int = 1) -> torch.Tensor:
     """``S <- diag(a) S + b v^T``, ``o = S^T q`` per (request, head), token after token.
     ``q, k [n, heads*dk]``, ``v [n, heads*dv]`` (rows may be slices), ``gates`` fp32 (``[n, heads*dk]``
     in mode ``GATED_LINEAR``, ``[n, 2*heads]`` = input | forget in mode ``EXP_GATED``).  ``state`` is
@@ -167,7 +168,10 @@ def matrix_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor | None, v: tor
     carries the normaliser) and ``mstate [slots, heads]`` the running maximum.  Returns fp32
     ``[n, heads * cols]``: ``cols = dv``, or ``dv + 2`` in mode ``EXP_GATED``, the two extra columns
     being ``n . q`` and ``exp(-m)``.  ``max_q_len`` 1 says that every request brings one token: the kernel laid
-    out for single tokens runs then."""
+    out for single tokens runs then.  Mode ``STEP_SIZED`` (the recurrence of state-space duality): ``gates [n, heads]``
+    are raw step sizes, ``gate_bias [heads]`` their bias, ``lower [heads]`` holds ``A = -exp(A_log)``;
+    ``dt = softplus(gates + gate_bias)``, ``a = exp(A dt)`` for the whole head, ``b = dt * k``; ``q`` and ``k`` are
+    ``[n, (heads / heads_per_group) * dk]``: ``heads_per_group`` neighbouring heads share them."""
     _rows(q, "q")
     _rows(v, "v", q.dtype)
     if k is not None:
@@ -179,10 +183,18 @@ def matrix_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor | None, v: tor
     extra = 1 if mode == EXP_GATED else 0
     if tuple(state.shape[1:]) != (heads, dv + extra, dk):
         raise ValueError("the recurrence's state does not fit its heads")
+    if heads_per_group != 1 and mode != STEP_SIZED:
+        raise ValueError("only the step-sized recurrence shares queries and keys between heads")
     if mode == EXP_GATED:
         _cuda(mstate, "mstate", torch.float32)
         if k is None or gates.shape[1] != 2 * heads:
             raise ValueError("the exponential-gate recurrence takes keys and two gates per head")
+    elif mode == STEP_SIZED:
+        _cuda(lower, "lower", torch.float32)
+        if (k is None or gates.shape[1] != heads or gate_bias.numel() != heads or lower.numel() != heads
+                or heads % heads_per_group or q.shape[1] != heads // heads_per_group * dk or k.shape[1] != q.shape[1]):
+            raise ValueError("the step-sized recurrence takes keys, one step size, bias and rate per head, and queries "
+                             "and keys of heads / heads_per_group groups")
     else:
         _cuda(lower, "lower", torch.float32)
     cols = dv + 2 * extra
@@ -193,9 +205,47 @@ def matrix_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor | None, v: tor
     _check(f(int(mode), q.data_ptr(), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0, v.data_ptr(),
              v.stride(0), gates.data_ptr(), gates.stride(0), gate_bias.data_ptr(), _ptr(lower), float(cap),
              float(q_scale), state.data_ptr(), _ptr(mstate), _ptr(work), cu_q.data_ptr(), state_slots.data_ptr(),
-             out.data_ptr(), out.stride(0), int(num_requests), int(max_q_len), heads, dk, dv, _stream()),
-           "matrix_recurrence")
+             out.data_ptr(), out.stride(0), int(num_requests), int(max_q_len), heads, dk, dv, int(heads_per_group),
+             _stream()), "matrix_recurrence")
     return out
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, groups: int, eps: float,
+                     skip: torch.Tensor | None = None, x: torch.Tensor | None = None, head_width: int = 0) -> torch.Tensor:
+    """``u = (y + skip[head] * x) * silu(z)`` (the skip term with ``skip`` ``[heads]`` fp32 and ``x``, head ``c //
+    head_width`` owning column ``c``), then every one of ``groups`` equal parts of a row divided by its own root mean
+    square (eps inside the root), times ``weight``: a norm whose gate comes BEFORE it.  ``y`` fp32 ``[n, width]``;
+    ``z``, ``x`` of the activation type (rows may be slices).  Returns ``[n, width]`` of the activation type."""
+    _rows(y, "y", torch.float32)
+    _rows(z, "z")
+    _cuda(weight, "weight", torch.float32)
+    n, width = y.shape
+    if z.shape != y.shape or weight.numel() != width or groups < 1 or width % groups:
+        raise ValueError("gated_group_norm's operands do not fit together")
+    if skip is not None:
+        _cuda(skip, "skip", torch.float32)
+        _rows(x, "x", z.dtype)
+        if x.shape != y.shape or head_width < 1 or skip.numel() * head_width != width:
+            raise ValueError("the skip term needs one factor per head and the recurrence's input")
+    out = torch.empty((n, width), dtype=z.dtype, device=y.device)
+    f = _fn("recurrent", f"gllm_gated_group_norm_{_suffix(z.dtype)}")
+    _check(f(y.data_ptr(), y.stride(0), _ptr(x) if skip is not None else None, x.stride(0) if skip is not None else 0,
+             _ptr(skip), int(head_width), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0),
+             n, int(groups), width // groups, float(eps), _stream()), "gated_group_norm")
+    return out
+
+
+def conv_state_advance(x: torch.Tensor, conv_state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor,
+                       num_requests: int) -> None:
+    """Bring ``conv_state [slots, taps-1, channels]`` (every request's last inputs of a short convolution, oldest
+    first) up to date with this step's inputs ``x [n, channels]`` (rows may be slices)."""
+    _rows(x, "x")
+    _cuda(conv_state, "conv_state", torch.float32)
+    if conv_state.shape[2] != x.shape[1]:
+        raise ValueError("the convolution's state does not fit the channels")
+    f = _fn("recurrent", f"gllm_conv_state_advance_{_suffix(x.dtype)}")
+    _check(f(x.data_ptr(), x.stride(0), conv_state.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(),
+             int(num_requests), x.shape[1], conv_state.shape[1] + 1, _stream()), "conv_state_advance")
 
 
 def head_norm(o: torch.Tensor, heads: int, dv: int, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,

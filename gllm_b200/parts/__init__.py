@@ -26,7 +26,7 @@ from gllm_b200.parts.base import (
     register_position_encoding,
 )
 from gllm_b200.parts import (  # noqa: F401  (register the built-in kinds)
-    attention, block, delta_rule, experts, hyper, latent_attention, mamba, matrix_memory, mlp, norm, parallel, rotary,
+    attention, block, delta_rule, differential_attention, experts, hyper, latent_attention, mamba, matrix_memory, mlp, norm, parallel, rotary,
     sigmoid_attention,
 )
 

@@ -42,3 +42,34 @@ class RMSNorm(Norm):
 
     def forward(self, branch, resid, dtype, rows=None):
         return ops.add_rmsnorm(branch, resid, self.weight, self.eps, dtype, rows=rows, unit_offset=self.unit_offset)
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh(Norm):
+    """``y = tanh(alpha * x) * weight + bias`` with one learned number ``alpha``: a norm that computes no mean and
+    no variance, fused with the residual add like the RMS norm (``csrc/dyt_norm.cu``).  Tensor names: ``weight``,
+    ``bias`` (one value per column), ``alpha`` (a single number)."""
+
+    graph_safe_portions = True
+
+    def __init__(self, names, size: int):
+        super().__init__(names)
+        self.size = int(size)
+        self.weight = self.bias = self.alpha = None
+
+    def kernel_needs(self):
+        return {"modules": {"dyt_norm"}}
+
+    def expected_tensors(self):
+        return {
+            self.names["weight"]: TensorExpectation((self.size,), "vector"),
+            self.names["bias"]: TensorExpectation((self.size,), "bias"),
+            self.names["alpha"]: TensorExpectation((), "vector"),
+        }
+
+    def load(self, get, dtype, device):
+        self.weight, self.bias = get(self.names["weight"], "vector"), get(self.names["bias"], "bias")
+        self.alpha = get(self.names["alpha"], "vector").reshape(1).contiguous()
+
+    def forward(self, branch, resid, dtype, rows=None):
+        return ops.add_dyt(branch, resid, self.alpha, self.weight, self.bias, dtype, rows=rows)
