@@ -82,12 +82,13 @@ def difference_weight(m, w, pre):
             + float(m["diff"]))
 
 
-def differential_attention(h, p, m, w, pre, eps, k, v):
-    """Two softmax maps over the same values, subtracted; per-head norm; gate; output projection."""
-    T, H, G, d, dv = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = rotate_pairs((h @ w[pre + ".q"].T).view(T, H * 2, d), p, m["rot"]).view(T, H, 2, d)
-    lam, cap, diff = difference_weight(m, w, pre), float(m["softcap"]), float(m["diff"])
-    visible = p[None, :] <= p[:, None]
+def attend(q, k, v, q_pos, k_pos, m, lam, eps, gate=None):
+    """``q [Tq, H, 2, dim]`` (rotated), ``k [Tk, G, 2, dim]`` (rotated), ``v [Tk, G, vdim]``: two capped softmax maps
+    per head over the keys at positions up to the query's, their difference, the per-head norm, the gate.
+    Returns ``[Tq, H * vdim]``."""
+    H, G = q.shape[1], k.shape[1]
+    cap, diff = float(m["softcap"]), float(m["diff"])
+    visible = k_pos[None, :] <= q_pos[:, None]
     heads = []
     for hd in range(H):
         g = hd // (H // G)
@@ -98,9 +99,16 @@ def differential_attention(h, p, m, w, pre, eps, k, v):
             s = s.masked_fill(~visible, -math.inf)
             maps.append(torch.softmax(s, -1) @ v[:, g])
         o = maps[0] - lam * maps[1]
-        o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * (1.0 - diff)
-        heads.append(o)
-    o = torch.cat(heads, -1) * sigmoid(h @ w[pre + ".g"].T)
+        heads.append(o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * (1.0 - diff))
+    o = torch.cat(heads, -1)
+    return o if gate is None else o * sigmoid(gate)
+
+
+def differential_attention(h, p, m, w, pre, eps, k, v):
+    """Queries of this layer over the given keys and values; gate; output projection."""
+    T, H, d = h.shape[0], m["heads"], m["dim"]
+    q = rotate_pairs((h @ w[pre + ".q"].T).view(T, H * 2, d), p, m["rot"]).view(T, H, 2, d)
+    o = attend(q, k, v, p, p, m, difference_weight(m, w, pre), eps, gate=h @ w[pre + ".g"].T)
     return o @ w[pre + ".o"].T
 
 
