@@ -60,6 +60,7 @@ MODULES = {
     "moe": "moe.cu",
     "dyt_norm": "dyt_norm.cu",
     "attention_diff": "attention_diff.cu",
+    "attention_diff_mma": "attention_diff_mma.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

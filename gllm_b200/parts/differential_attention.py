@@ -57,7 +57,7 @@ class DifferentialAttention(Mixer):
         self.lam = 0.0
 
     def kernel_needs(self):
-        return {"modules": {"attention_diff"}}
+        return {"modules": {"attention_diff", "attention_diff_mma"}}
 
     def kv_requirement(self):
         return KVPageRequirement(((self.kv_heads, 2 * self.dk), (self.kv_heads, self.dv)), None)

@@ -232,6 +232,90 @@ def test_differential_attention_kernels(heads, kv_heads, dim, vdim, dims, page):
         assert float((want[0][-20:] - plain_rows(muted)[-20:]).abs().max()) > 0.05
 
 
+class _Step:
+    """What the tensor-core attention reads of a step: per-request lengths and slots, and the step's scratch."""
+
+    def __init__(self, lengths, starts, slots):
+        from gllm_b200.engine.step import Workspace
+
+        dev = "cuda"
+        self.cu_q = torch.tensor([0] + list(np.cumsum(lengths)), dtype=torch.int32, device=dev)
+        self.context_lens = torch.tensor(starts, dtype=torch.int32, device=dev)
+        self.state_slots = torch.tensor(slots, dtype=torch.int32, device=dev)
+        self.num_requests, self.max_q_len = len(lengths), max(lengths)
+        self.max_seq_len = max(s + n for s, n in zip(starts, lengths))
+        self.workspace = Workspace(dev)
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,dims,page", [(4, 2, 64, 64, 32, 16), (3, 1, 32, 96, 32, 8),
+                                                              (2, 2, 128, 128, 64, 16), (8, 2, 64, 128, 16, 32),
+                                                              (5, 5, 32, 32, 0, 16)])
+def test_differential_attention_on_the_tensor_cores(heads, kv_heads, dim, vdim, dims, page):
+    """The bf16 kernel pair (tiles of 64 keys, two maps as two sets of CTAs, the combining kernel) against the plain
+    functions on the same bf16 inputs: two requests in portions and single tokens over shuffled pages, then single
+    tokens over a context long enough that every request's keys are cut into ranges that are merged afterwards."""
+    from gllm_b200.ops import differential
+
+    g = torch.Generator().manual_seed(heads * 1000 + dim)
+    m = _att(heads, kv_heads, dim, vdim, 0.5 * dim ** -0.5, dims, softcap=5.0, diff=0.35, base=300.0,
+             scaling=(4.0, 1.0, 4.0, 32) if dims else None)
+    lam, eps = 0.55, 1e-5
+    total = {0: 700, 1: 150}
+    qw, kw, gw = heads * 2 * dim, kv_heads * 2 * dim, heads * vdim
+    proj = {r: (torch.randn(n, qw + kw + kv_heads * vdim + gw, generator=g) * 1.5).to(torch.bfloat16)
+            for r, n in total.items()}
+    pages_per = {r: -(-n // page) for r, n in total.items()}
+    n_pages = sum(pages_per.values()) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((4, max(pages_per.values())), -1, dtype=torch.int32)
+    slot_of = {0: 2, 1: 0}
+    for r in total:
+        for i in range(pages_per[r]):
+            table[slot_of[r], i] = order.pop()
+    inv_freq = plain.scaled_frequencies(m["rot"]).to(torch.float32).cuda() if dims else None
+
+    def plain_rows(rows):
+        T = rows.shape[0]
+        x, p = rows.to(F), torch.arange(T)
+        bf = lambda t: t.to(torch.bfloat16).to(F)                       # what the kernel reads back is bf16
+        q = bf(plain.rotate_pairs(x[:, :qw].reshape(T, heads * 2, dim), p, m["rot"])).view(T, heads, 2, dim)
+        k = bf(plain.rotate_pairs(x[:, qw:qw + kw].reshape(T, kv_heads * 2, dim), p, m["rot"])).view(T, kv_heads, 2, dim)
+        v = x[:, qw + kw: qw + kw + kv_heads * vdim].view(T, kv_heads, vdim)
+        return plain.attend(q, k, v, p, p, m, lam, eps, gate=x[:, -gw:])
+
+    want = {r: plain_rows(proj[r]) for r in total}
+    cache = torch.zeros(n_pages, page * kv_heads * (2 * dim + vdim), device="cuda", dtype=torch.bfloat16)
+    done = {0: 0, 1: 0}
+    got = {r: [] for r in total}
+    plans = [[(0, 200), (1, 70)], [(1, 1), (0, 2)], [(0, 1), (1, 1)], [(0, 129), (1, 63)], [(0, 360)]]
+    plans += [[(0, 1), (1, 1)]] * 6 + [[(0, 1)]] + [[(1, 9), (0, 1)]]
+    split_steps = 0
+    for plan in plans:
+        lengths, starts = [n for _, n in plan], [done[r] for r, _ in plan]
+        _, pos, row = _batch(lengths, starts, [slot_of[r] for r, _ in plan])
+        step = _Step(lengths, starts, [slot_of[r] for r, _ in plan])
+        x = torch.cat([proj[r][done[r]:done[r] + n] for r, n in plan]).cuda()
+        slot_map = torch.cat([torch.tensor([int(table[slot_of[r], t // page]) * page + t % page
+                                            for t in range(done[r], done[r] + n)]) for r, n in plan])
+        differential.diff_rope_store(x, pos, inv_freq, dims, True, slot_map.to(torch.int32).cuda(), cache, heads,
+                                     kv_heads, dim, vdim, True, page)
+        out = differential.differential_attention(x, x[:, -gw:], cache, table.cuda(), pos, row, heads, kv_heads, dim,
+                                                  vdim, page, m["scale"], m["softcap"], lam, eps, 1.0 - m["diff"],
+                                                  batch=step)
+        split_steps += step.max_q_len == 1 and step.max_seq_len > 2 * differential.SPLIT_KEYS
+        at = 0
+        for r, n in plan:
+            got[r].append(out[at:at + n].double().cpu())
+            at += n
+            done[r] += n
+    assert split_steps >= 5
+    for r in total:
+        g_all = torch.cat(got[r])
+        assert g_all.shape[0] == done[r] <= total[r]
+        err = (g_all - want[r][:done[r]]).abs()
+        assert float(err.max()) < 0.06 and float(err.mean()) < 0.006, (r, float(err.max()), float(err.mean()))
+
+
 @pytest.mark.parametrize("experts,top,groups,keep,scale", [(16, 4, 4, 3, 2.0), (8, 2, 4, 2, 1.5), (6, 1, 1, 1, 1.0),
                                                            (4, 4, 2, 2, 0.5), (8, 3, 2, 1, 2.5), (40, 8, 8, 4, 1.0)])
 def test_router_with_softmax_scores_and_group_maxima(experts, top, groups, keep, scale):
