@@ -561,7 +561,38 @@ def mifidra_raw(sz: dict) -> dict:
             "torch_dtype": "bfloat16"}
 
 
-DESIGNS = {"guvetar": guvetar_raw, "rulunex": rulunex_raw, "mifidra": mifidra_raw}
+def sazisun_raw(sz: dict) -> dict:
+    """``layers`` layers: state-space duality and differential attention in turn, every third attention layer
+    reading the keys and values of the attention layer before it; dense feed-forwards alternate with routed experts
+    (16 experts of ff/4 without a gate, 4 per token from 3 of 4 groups, beside a shared expert of ff/2: as many active
+    feed-forward weights per token as the gated dense layers).  The attention has half of Llama's heads with two
+    maps of ``head_dim`` each and values of twice that width: projections of Llama's sizes."""
+    heads, kv_heads, dim = sz["heads"] // 2, max(1, sz["kv_heads"] // 2), sz["head_dim"]
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5,
+                 "softcap": 50.0, "diff": 0.5,
+                 "rot": {"base": 10000.0, "dims": dim,
+                         "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}
+    ssd = {"heads": sz["inner"] // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": sz["ff"] // 4}, "shared": {"ff": sz["ff"] // 2},
+              "router": {"experts": 16, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 3}}}
+    layers, owner, readers = [], None, 0
+    for i in range(sz["layers"]):
+        if i % 2 == 0:
+            layers.append({"type": "mamba2", "mixer": dict(ssd), "mlp": dense})
+            continue
+        mixer = dict(attention)
+        if owner is not None and readers == 0:
+            mixer["kv_from"] = owner
+            readers += 1
+        else:
+            owner, readers = i, 0
+        layers.append({"type": "attention", "mixer": mixer, "mlp": routed})
+    return {"architecture": "Sazisun", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-5},
+            "layers": layers, "torch_dtype": "bfloat16"}
+
+
+DESIGNS = {"guvetar": guvetar_raw, "rulunex": rulunex_raw, "mifidra": mifidra_raw, "sazisun": sazisun_raw}
 
 
 def llama_raw(sz: dict) -> dict:

@@ -460,7 +460,100 @@ def routed_experts(tokens=2048, width=2048, ff=1024, experts=16, top=4, groups=4
                    6.0 * tokens * top * ff * width)
 
 
+def differential_attention(tokens=2048, batch=1, context=0, hq=16, hkv=4, dk=64, dv=128, block_size=16, iters=5,
+                           peaks=None, mma=1):
+    """``batch`` requests of ``tokens`` new tokens over ``context`` cached ones (tokens=1: a decode step): both maps,
+    the difference, the per-head norm and the gate."""
+    from gllm_b200.ops import differential
+
+    differential.USE_TENSOR_CORES = bool(mma)
+    pages_per_req = -(-(context + tokens) // block_size)
+    num_pages = batch * pages_per_req + 1
+    g = torch.Generator(device="cuda").manual_seed(0)
+    pool = torch.randn((num_pages, block_size * hkv * (2 * dk + dv)), generator=g, device="cuda").to(torch.bfloat16)
+    table = torch.randperm(num_pages - 1, generator=g, device="cuda").to(torch.int32).view(batch, pages_per_req).contiguous()
+    proj = torch.randn(batch * tokens, hq * 2 * dk + hq * dv, device="cuda").to(torch.bfloat16)
+    b = _Batch(batch, tokens, context)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: differential.differential_attention(proj, proj[:, hq * 2 * dk:], pool, table, b.positions, b.token_row,
+                                                     hq, hkv, dk, dv, block_size, dk ** -0.5, 50.0, 0.4, 1e-5, 0.5,
+                                                     batch=b)
+    us = _time(fn, iters, flush)
+    flops = 2.0 * 2 * (dk + dv) * hq * batch * (tokens * context + tokens * (tokens + 1) / 2)
+    nbytes = batch * (context + tokens) * hkv * (2 * dk + dv) * 2 + proj.numel() * 2 + batch * tokens * hq * dv * 2
+    return _result("differential_attention (mma.sync)" if mma else "differential_attention (CUDA cores)", us, peaks,
+                   dict(tokens=tokens, batch=batch, context=context, heads=hq, kv_heads=hkv, dk=dk, dv=dv), nbytes, flops)
+
+
+def step_sized_recurrence(tokens=2048, batch=1, heads=64, dk=128, dv=64, groups=1, norm=0, iters=5, peaks=None):
+    """The recurrence of state-space duality (``norm=1``: the gated norm over the whole row behind it instead)."""
+    from gllm_b200.ops import stateful
+
+    n, inner = batch * tokens, heads * dv
+    xbc = torch.randn(n, inner + 2 * groups * dk, device="cuda").to(torch.bfloat16)
+    z = torch.randn(n, inner, device="cuda").to(torch.bfloat16)
+    dt = torch.randn(n, heads, device="cuda")
+    dt_bias, A, D = torch.zeros(heads, device="cuda"), -torch.rand(heads, device="cuda"), torch.ones(heads, device="cuda")
+    w = torch.ones(inner, device="cuda")
+    state = torch.zeros(batch + 1, heads, dv, dk, device="cuda")
+    b = _Batch(batch, tokens, 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    gn = groups * dk
+    rec = lambda: stateful.matrix_recurrence(stateful.STEP_SIZED, xbc[:, inner + gn:], xbc[:, inner:inner + gn],
+                                             xbc[:, :inner], dt, dt_bias, A, 0.0, 1.0, state, None, b.cu_q, b.state_slots,
+                                             batch, heads, dk, dv, max_q_len=tokens, heads_per_group=heads // groups)
+    if norm:
+        y = rec()
+        fn = lambda: stateful.gated_group_norm(y, z, w, 1, 1e-5, skip=D, x=xbc[:, :inner], head_width=dv)
+        us = _time(fn, iters, flush)
+        return _result("gated_group_norm", us, peaks, dict(tokens=tokens, batch=batch, width=inner),
+                       n * inner * (4 + 2 + 2 + 2) + inner * 4)
+    us = _time(rec, iters, flush)
+    nbytes = 2 * batch * heads * dk * dv * 4 + n * (xbc.shape[1] * 2 + heads * 4 + inner * 4)
+    return _result("matrix_recurrence (step sizes)", us, peaks, dict(tokens=tokens, batch=batch, heads=heads, dk=dk, dv=dv),
+                   nbytes, 4.0 * n * heads * dk * dv)
+
+
+def add_dyt(rows=2048, hidden=2048, iters=5, peaks=None):
+    from gllm_b200 import ops
+
+    resid = torch.randn(rows, hidden, device="cuda")
+    branch = torch.randn(rows, hidden, device="cuda").to(torch.bfloat16)
+    alpha, w, bias = torch.ones(1, device="cuda"), torch.ones(hidden, device="cuda"), torch.zeros(hidden, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    us = _time(lambda: ops.add_dyt(branch, resid, alpha, w, bias, torch.bfloat16), iters, flush)
+    return _result("add_dyt", us, peaks, dict(rows=rows, hidden=hidden), rows * hidden * (4 + 4 + 2 + 2) + hidden * 8)
+
+
+def ungated_experts(tokens=2048, width=2048, ff=2048, experts=16, top=4, groups=4, keep=3, mma=1, iters=5, peaks=None):
+    """Softmax routing, sorting the pairs by expert, both products of experts without a gate (``down(relu(up x)^2)``)
+    and the weighted sum of ``tokens`` tokens (``mma=0``: the CUDA-core products)."""
+    from gllm_b200.ops import moe
+
+    x = (torch.randn(tokens, width, device="cuda") * 0.5).to(torch.bfloat16)
+    w_up = (torch.randn(experts, ff, width, device="cuda") * width ** -0.5).to(torch.bfloat16)
+    w_d = (torch.randn(experts, width, ff, device="cuda") * ff ** -0.5).to(torch.bfloat16)
+    logits = torch.randn(tokens, experts, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    tensor_cores = bool(mma) and moe.tensor_cores_take(torch.bfloat16, width, ff, gated=False)
+
+    def fn():
+        ids, weights = moe.route(logits, None, top, groups, keep, True, score="softmax", group_score="max",
+                                 renormalize_eps=1e-20, scale=2.0)
+        return moe.apply_experts(x, ids, weights, w_up, w_d, None, tensor_cores, gated=False)
+
+    us = _time(fn, iters, flush)
+    used = min(experts, tokens * top)
+    nbytes = used * 2 * ff * width * 2 + tokens * width * 4 + tokens * top * (ff * 6 + width * 8)
+    return _result("ungated_experts", us, peaks, dict(tokens=tokens, width=width, ff=ff, experts=experts, top=top), nbytes,
+                   4.0 * tokens * top * ff * width)
+
+
 KERNELS = {
+    "differential_attention": differential_attention,
+    "step_sized_recurrence": step_sized_recurrence,
+    "add_dyt": add_dyt,
+    "ungated_experts": ungated_experts,
     "attention_decode": attention_decode,
     "attention_prefill": attention_prefill,
     "linear": linear,

@@ -129,3 +129,5 @@ def test_presets_parse():
     assert (cfg.num_hidden_layers, cfg.hidden_size, cfg.vocab_size, cfg.head_dim) == (16, 2048, 128256, 64)
     assert cfg.rope_scaling.factor == 32.0 and cfg.tie_word_embeddings
     assert not load_config(load_preset("llama-3.1-8b")).tie_word_embeddings
+    wide = load_config(load_preset("sazisun-w2048"))
+    assert wide.architecture == "Sazisun" and wide.hidden_size == 2048 and wide.layers[3].mixer["kv_from"] == 1
