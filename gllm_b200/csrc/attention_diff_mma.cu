@@ -17,6 +17,7 @@
 
 namespace {
 constexpr int BM = 64, BN = 64, DM_THREADS = 128;
+static_assert(DM_THREADS == 2 * BN, "two threads fetch a key");
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1e30f;
 
@@ -100,34 +101,33 @@ diff_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, float* __
           q + (int64_t)(tok_begin + t0 + (ok ? tl : 0)) * q_stride + (int64_t)((h0 + g) * 2 + map) * DK + piece * 8;
       cp_async16(smem_u32(q_sm + (rr * CK + swz<CK>(rr, piece)) * 16), src, ok);
     }
+    // two threads a key: one page look-up each, then the key's 16-byte pieces in turn (keys first, values after)
     auto load_kv = [&](int tile, int stage) {
       unsigned char* k_dst = kv_sm + stage * (K_BYTES + V_BYTES);
       unsigned char* v_dst = k_dst + K_BYTES;
-      for (int idx = threadIdx.x; idx < BN * (CK + CV); idx += DM_THREADS) {
-        const int row = idx / (CK + CV), piece = idx - row * (CK + CV);
-        const int key = tile * BN + row;
-        bool ok = key <= pos_last;
-        int page = 0;
-        if (ok) {
-          page = bt[key / block_size];
-          if (page < 0 || page >= num_pages) {
-            atomicOr(status, GLLM_STATUS_PAGE_RANGE);
-            ok = false;
-            page = 0;
-          }
-        }
-        const int off = key % block_size;
-        if (piece < CK) {
-          const __nv_bfloat16* src = cache + (int64_t)page * page_elems +
-                                     ((int64_t)kvh * block_size + off) * 2 * DK + map * DK + piece * 8;
-          cp_async16(smem_u32(k_dst + (row * CK + swz<CK>(row, piece)) * 16), ok ? src : cache, ok);
-        } else {
-          const int pv = piece - CK;
-          const __nv_bfloat16* src =
-              cache + (int64_t)page * page_elems + v_region + ((int64_t)kvh * block_size + off) * DV + pv * 8;
-          cp_async16(smem_u32(v_dst + (row * CV + swz<CV>(row, pv)) * 16), ok ? src : cache, ok);
+      const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+      const int key = tile * BN + row;
+      bool ok = key <= pos_last;
+      int page = 0;
+      if (ok) {
+        page = bt[key / block_size];
+        if (page < 0 || page >= num_pages) {
+          atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+          ok = false;
+          page = 0;
         }
       }
+      const int off = key % block_size;
+      const __nv_bfloat16* k_src =
+          ok ? cache + (int64_t)page * page_elems + ((int64_t)kvh * block_size + off) * 2 * DK + map * DK : cache;
+      const __nv_bfloat16* v_src =
+          ok ? cache + (int64_t)page * page_elems + v_region + ((int64_t)kvh * block_size + off) * DV : cache;
+#pragma unroll
+      for (int piece = half; piece < CK; piece += 2)
+        cp_async16(smem_u32(k_dst + (row * CK + swz<CK>(row, piece)) * 16), ok ? k_src + piece * 8 : cache, ok);
+#pragma unroll
+      for (int piece = half; piece < CV; piece += 2)
+        cp_async16(smem_u32(v_dst + (row * CV + swz<CV>(row, piece)) * 16), ok ? v_src + piece * 8 : cache, ok);
     };
     load_kv(tile_first, 0);
     cp_async_commit();

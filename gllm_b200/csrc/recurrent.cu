@@ -355,7 +355,7 @@ matrix_recurrence_kernel(int,
   float* sp = state + (((int64_t)slot * heads + h) * dvx + (live ? col : 0)) * dk;
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
-    const int d = sub * DPT + i;
+    const int d = ((i >> 2) * lanes + sub) * 4 + (i & 3);
     S[i] = (live && d < dk) ? sp[d] : 0.f;
   }
 
@@ -481,8 +481,10 @@ matrix_recurrence_kernel(int,
     const int nt_next = min(tc, end - next);
     if (next < end) fetch(next, nt_next);
     const float* buf = bufs + which * buf_floats;
-    const float* q_s = buf + sub * DPT;
-    const float* g_s = buf + tc * dkp + sub * DPT;
+    // a thread's key channels come in fours, `lanes` fours apart: the threads of a column then read neighbouring
+    // 16 bytes of the staged operands (one four-float load each, no two on one bank)
+    const float* q_s = buf + sub * 4;
+    const float* g_s = buf + tc * dkp + sub * 4;
     const float* v_s = buf + 2 * tc * dkp;
     const float* sc_s = v_s + tc * cols;
     float* out_p = out + (int64_t)t0 * out_stride + (int64_t)h * out_cols;
@@ -499,7 +501,7 @@ matrix_recurrence_kernel(int,
       const float4* g4 = reinterpret_cast<const float4*>(g_s + tt * dkp);
 #pragma unroll
       for (int i4 = 0; i4 < DPT / 4; ++i4) {
-        const float4 qq = q4[i4], gg = g4[i4];
+        const float4 qq = q4[i4 * lanes], gg = g4[i4 * lanes];
         const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ga[4] = {gg.x, gg.y, gg.z, gg.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -523,7 +525,7 @@ matrix_recurrence_kernel(int,
   if (live) {
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-      const int d = sub * DPT + i;
+      const int d = ((i >> 2) * lanes + sub) * 4 + (i & 3);
       if (d < dk) sp[d] = S[i];
     }
   }

@@ -11,8 +11,9 @@ from gllm_b200.ops import _check, _cuda, _fn, _ptr, _stream, _suffix, status_wor
 
 # GLLM_B200_DIFF_MMA=0: the differential attention of bf16 models stays on the CUDA-core kernel (for measurements)
 USE_TENSOR_CORES = os.environ.get("GLLM_B200_DIFF_MMA", "1") != "0"
-SPLIT_KEYS = 256          # keys per CTA at least when single tokens' contexts are cut (a multiple of the key tile of 64)
-MAX_SPLITS = 16
+# keys per CTA at least when single tokens' contexts are cut (a multiple of the key tile of 64), and the most ranges
+SPLIT_KEYS = int(os.environ.get("GLLM_B200_DIFF_SPLIT_KEYS", "256"))
+MAX_SPLITS = int(os.environ.get("GLLM_B200_DIFF_MAX_SPLITS", "16"))
 
 _mma = None
 
