@@ -302,7 +302,8 @@ exp_gate_scan_kernel(const float* __restrict__ gates, int64_t gates_stride, cons
 // m' = max(f + m, i), a = exp(f + m - m'), b[d] = exp(i - m') * k[d], q = q_raw * q_scale; the state
 // has one column more than there are value columns, fed with ones, which carries the normaliser n, and
 // the output gets two columns more: n . q and exp(-m').  mode 2 (state-space duality): one step size per (token, head),
-// dt = softplus(dt_raw + dt_bias[h]); a = exp(A[h] * dt) for the whole head (A = -exp(A_log) arrives in `lower`),
+// dt = softplus(dt_raw + dt_bias[h]); a = exp(A[h] * dt) for the whole head (A = -exp(A_log) arrives in `lower`;
+// the update is written S += b v - (1 - a) S with 1 - a from expm1),
 // b[d] = dt * k[d] (k: the input projection B), q: the read-out projection C; heads share B and C in groups of
 // `kv_div` neighbouring heads.
 // A block owns `cols` columns of one (request, head); `lanes` threads share a column, each keeping DPT of its
@@ -464,7 +465,9 @@ matrix_recurrence_kernel(int,
     }
     if (mode == 2 && (int)threadIdx.x < nt) {
       const float dt = softplusf_(as_value<float>(pi) + gate_bias[h]);
-      sc_s[threadIdx.x] = expf(lower[h] * dt);                                               // keep
+      // what the state LOSES, 1 - exp(A dt), straight from expm1: a decay next to one rounds to a float 1e-7 off,
+      // and that error, made anew at every token, would add up over the hundreds of tokens such a state remembers
+      sc_s[threadIdx.x] = -expm1f(lower[h] * dt);                                            // 1 - keep
       sc_s[tc + threadIdx.x] = dt;                                                           // take
     }
   };
@@ -508,7 +511,8 @@ matrix_recurrence_kernel(int,
           const int i = i4 * 4 + e;
           const float a = mode >= 1 ? keep : ga[e];
           const float b = mode >= 1 ? take * ga[e] : 1.0f - ga[e];
-          S[i] = a * S[i] + b * vj;
+          if (mode == 2) S[i] += fmaf(b, vj, -(keep * S[i]));       // keep holds 1 - decay here
+          else S[i] = a * S[i] + b * vj;
           o = fmaf(S[i], qa[e], o);
         }
       }
@@ -634,7 +638,7 @@ matrix_recurrence_step_kernel(int mode, const T* __restrict__ q, int64_t q_strid
     take = expf(g[h] - m_new);
   } else if (mode == 2) {
     take = softplusf_(gates[t * gates_stride + h] + gate_bias[h]);          // the step size
-    keep = expf(lower[h] * take);
+    keep = -expm1f(lower[h] * take);                                        // what the state loses, 1 - decay
   }
   const float vj = !live ? 0.f : (col < dv ? to_float(v[t * v_stride + (int64_t)h * dv + col]) : 1.0f);
   float* sp = state + (((int64_t)slot * heads + h) * dvx + (live ? col : 0)) * dk;
@@ -665,7 +669,8 @@ matrix_recurrence_step_kernel(int mode, const T* __restrict__ q, int64_t q_strid
           b = 1.0f - a;
           qe = siluf_(to_float(q[t * q_stride + hd]));
         }
-        S[e] = a * S[e] + b * vj;
+        if (mode == 2) S[e] += fmaf(b, vj, -(keep * S[e]));
+        else S[e] = a * S[e] + b * vj;
         o = fmaf(S[e], qe, o);
       }
     }
