@@ -274,21 +274,23 @@ diff_combine_kernel(const float* __restrict__ partial, const float* __restrict__
   for (int i = 0; i < 8; ++i) o[i] = 0.f;
 #pragma unroll
   for (int map = 0; map < 2; ++map) {
-    float big = NEG_BIG;
-    for (int s = 0; s < splits; ++s) big = fmaxf(big, stats[(((int64_t)s * 2 + map) * per_map + item) * 2]);
-    float total = 0.f, a[8];
+    // lane s holds the maximum and sum of range s (at most 32 ranges): one load each, all at once
+    float2 st = make_float2(NEG_BIG, 0.f);
+    if (lane < splits) st = *reinterpret_cast<const float2*>(stats + ((((int64_t)lane * 2 + map) * per_map + item) * 2));
+    const float big = warp_max(st.y > 0.f ? st.x : NEG_BIG);
+    const float w_mine = st.y > 0.f ? exp2f(st.x - big) : 0.f;
+    const float total = warp_sum(st.y * w_mine);         // (lanes beyond the ranges add zeros)
+    float a[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) a[i] = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {                  // ascending ranges: one order of the sums
-      const int64_t at = ((int64_t)s * 2 + map) * per_map + item;
-      const float2 st = *reinterpret_cast<const float2*>(stats + at * 2);
-      if (st.y <= 0.f) continue;
-      const float w = exp2f(st.x - big);
-      total = fmaf(st.y, w, total);
+      const float w = __shfl_sync(0xffffffffu, w_mine, s);
+      const float* row = partial + (((int64_t)s * 2 + map) * per_map + item) * dv;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int c = lane + 32 * i;
-        if (c < dv) a[i] = fmaf(partial[at * dv + c], w, a[i]);
+        if (c < dv) a[i] = fmaf(row[c], w, a[i]);
       }
     }
     const float inv = total > 0.f ? (map == 0 ? 1.0f : -lambda) / total : 0.f;
@@ -355,7 +357,7 @@ GLLM_API int gllm_attention_diff_mma(const __nv_bfloat16* q, int64_t q_stride, c
   if (num_requests <= 0 || max_q_len <= 0 || n_tokens <= 0) return 0;
   if (hq <= 0 || hkv <= 0 || hq % hkv || num_requests > 65535 || (q_stride % 8) || splits < 1 ||
       (splits > 1 && tiles_per_split < 1) || partial == nullptr || stats == nullptr || !(softcap > 0.f) ||
-      (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15))
+      splits > 32 || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15))
     return (int)cudaErrorInvalidValue;
   int rc = (int)cudaErrorInvalidValue;
 #define GLLM_DM(A, B)                                                                                               \

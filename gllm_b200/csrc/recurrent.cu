@@ -729,7 +729,7 @@ head_norm_kernel(const float* __restrict__ o, int64_t o_stride, int o_cols, int 
 // y is the fp32 read-out of a recurrence, x its input and z the gate, both of the activation type.  The gate comes
 // BEFORE the norm, and the groups need not be heads.  Two passes over the group's columns; everything in fp32.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 gated_group_norm_kernel(const float* __restrict__ y, int64_t y_stride, const T* __restrict__ x, int64_t x_stride,
                         const float* __restrict__ skip, int head_width, const T* __restrict__ z, int64_t z_stride,
                         const float* __restrict__ w, T* __restrict__ out, int64_t out_stride, int group_width,
@@ -910,7 +910,11 @@ int gated_group_norm_launch(const float* y, int64_t y_stride, const T* x, int64_
   if (n_tokens <= 0) return 0;
   if (groups < 1 || groups > 65535 || group_width < 1 || (skip != nullptr && (x == nullptr || head_width < 1)))
     return (int)cudaErrorInvalidValue;
-  const int threads = group_width >= 256 ? 256 : (group_width + 31) / 32 * 32;
+  // wide groups of few tokens (single decoded tokens: a handful of blocks in all) get 1,024 threads a block, four
+  // columns a thread and pass; otherwise 256
+  const bool few = (int64_t)n_tokens * groups < 2 * gllm_sm_count();
+  const int cap = few ? 1024 : 256;
+  const int threads = group_width >= cap ? cap : (group_width + 31) / 32 * 32;
   return gllm_launch(gated_group_norm_kernel<T>, dim3(n_tokens, groups), dim3(threads), 0, stream, y, y_stride, x,
                      x_stride, skip, head_width, z, z_stride, w, out, out_stride, group_width, eps);
 }
