@@ -564,18 +564,18 @@ def mifidra_raw(sz: dict) -> dict:
 def sazisun_raw(sz: dict) -> dict:
     """``layers`` layers: state-space duality and differential attention in turn, every third attention layer
     reading the keys and values of the attention layer before it; dense feed-forwards alternate with routed experts
-    (16 experts of ff/4 without a gate, 4 per token from 3 of 4 groups, beside a shared expert of ff/2: as many active
+    (16 experts of ff/4 without a gate, 4 per token from 4 of 8 groups, beside a shared expert of ff/2: as many active
     feed-forward weights per token as the gated dense layers).  The attention has half of Llama's heads with two
     maps of ``head_dim`` each and values of twice that width: projections of Llama's sizes."""
     heads, kv_heads, dim = sz["heads"] // 2, max(1, sz["kv_heads"] // 2), sz["head_dim"]
     attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5,
-                 "softcap": 50.0, "diff": 0.5,
+                 "softcap": 30.0, "diff": 0.3,
                  "rot": {"base": 10000.0, "dims": dim,
-                         "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}
+                         "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     ssd = {"heads": sz["inner"] // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
     dense = {"kind": "dense", "ff": sz["ff"]}
     routed = {"kind": "moe", "expert": {"ff": sz["ff"] // 4}, "shared": {"ff": sz["ff"] // 2},
-              "router": {"experts": 16, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 3}}}
+              "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 8, "keep": 4}}}
     layers, owner, readers = [], None, 0
     for i in range(sz["layers"]):
         if i % 2 == 0:

@@ -476,7 +476,7 @@ def differential_attention(tokens=2048, batch=1, context=0, hq=16, hkv=4, dk=64,
     b = _Batch(batch, tokens, context)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     fn = lambda: differential.differential_attention(proj, proj[:, hq * 2 * dk:], pool, table, b.positions, b.token_row,
-                                                     hq, hkv, dk, dv, block_size, dk ** -0.5, 50.0, 0.4, 1e-5, 0.5,
+                                                     hq, hkv, dk, dv, block_size, dk ** -0.5, 30.0, 0.4, 1e-5, 0.7,
                                                      batch=b)
     us = _time(fn, iters, flush)
     flops = 2.0 * 2 * (dk + dv) * hq * batch * (tokens * context + tokens * (tokens + 1) / 2)
@@ -525,7 +525,7 @@ def add_dyt(rows=2048, hidden=2048, iters=5, peaks=None):
     return _result("add_dyt", us, peaks, dict(rows=rows, hidden=hidden), rows * hidden * (4 + 4 + 2 + 2) + hidden * 8)
 
 
-def ungated_experts(tokens=2048, width=2048, ff=2048, experts=16, top=4, groups=4, keep=3, mma=1, iters=5, peaks=None):
+def ungated_experts(tokens=2048, width=2048, ff=2048, experts=16, top=4, groups=8, keep=4, mma=1, iters=5, peaks=None):
     """Softmax routing, sorting the pairs by expert, both products of experts without a gate (``down(relu(up x)^2)``)
     and the weighted sum of ``tokens`` tokens (``mma=0``: the CUDA-core products)."""
     from gllm_b200.ops import moe
@@ -539,7 +539,7 @@ def ungated_experts(tokens=2048, width=2048, ff=2048, experts=16, top=4, groups=
 
     def fn():
         ids, weights = moe.route(logits, None, top, groups, keep, True, score="softmax", group_score="max",
-                                 renormalize_eps=1e-20, scale=2.0)
+                                 renormalize_eps=1e-20, scale=2.5)
         return moe.apply_experts(x, ids, weights, w_up, w_d, None, tensor_cores, gated=False)
 
     us = _time(fn, iters, flush)

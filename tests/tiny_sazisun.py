@@ -70,7 +70,7 @@ SAZISUN_B = {
     "architecture": "Sazisun", "vocab": 131, "width": 48, "norm": {"eps": 1e-6},
     "layers": [
         _layer(_ssd(3, 10, 12, 1, 2, 1), None),
-        _layer(_att(3, 1, 10, 6, 0.35, 10, softcap=50.0, diff=0.1, base=500.0), _moe(20, 6, 1, 1.0)),
+        _layer(_att(3, 1, 10, 6, 0.35, 10, softcap=45.0, diff=0.1, base=500.0), _moe(20, 6, 1, 1.0)),
         _layer(_ssd(2, 24, 8, 2, 1, 4), _dense(40)),
         _layer(_att(1, 1, 12, 20, 0.3, 0, softcap=12.0, diff=0.5), _dense(56)),
     ],
