@@ -95,7 +95,7 @@ def test_the_norm_without_a_statistic(dtype, rows, width):
 
 @pytest.mark.parametrize("heads,vdim,state,groups,taps,norm_groups", [
     (4, 16, 16, 2, 4, 2), (3, 10, 12, 1, 2, 1), (2, 24, 8, 2, 1, 4), (8, 64, 128, 1, 4, 8), (2, 6, 160, 2, 3, 3),
-    (6, 32, 64, 6, 2, 1), (1, 40, 20, 1, 4, 5)])
+    (6, 32, 64, 6, 2, 1), (1, 40, 20, 1, 4, 5), (2, 8, 6, 1, 2, 2), (5, 12, 33, 5, 3, 1), (2, 16, 300, 2, 2, 1)])
 def test_step_sized_recurrence_kernels(heads, vdim, state, groups, taps, norm_groups):
     """The convolution with its state, the recurrence with one step size per head and token (heads sharing their
     input and read-out projections in groups) and the gated norm over groups of columns, for two requests in three
