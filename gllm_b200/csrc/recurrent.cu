@@ -311,6 +311,10 @@ exp_gate_scan_kernel(const float* __restrict__ gates, int64_t gates_stride, cons
 // by the instructions a warp spends per token, so the state is spread over many threads).  Tokens are taken in chunks of `tc`: while a chunk is computed from shared memory, the raw
 // inputs of the next one are on their way into registers; they are turned into the effective q, gate (or
 // key) and v and put into the other buffer afterwards.
+#ifndef REC_TOKEN_UNROLL
+#define REC_TOKEN_UNROLL 2            // tokens of a chunk whose instructions the compiler may interleave
+#endif
+constexpr int REC_UNROLL_TOKENS = REC_TOKEN_UNROLL;
 constexpr int REC_THREADS = 256;
 constexpr int REC_MAX_CHUNK = 16;
 constexpr int REC_LOOKAHEAD = 2048; // values of one operand that a block fetches ahead per chunk (8 per thread)
@@ -491,7 +495,7 @@ matrix_recurrence_kernel(int,
     const float* v_s = buf + 2 * tc * dkp;
     const float* sc_s = v_s + tc * cols;
     float* out_p = out + (int64_t)t0 * out_stride + (int64_t)h * out_cols;
-#pragma unroll 2
+#pragma unroll REC_UNROLL_TOKENS
     for (int tt = 0; tt < nt; ++tt) {
       const float vj = v_s[tt * cols + cix];
       float keep = 0.f, take = 0.f;
